@@ -49,7 +49,7 @@ class LayerSpec:
     the checkpoint's tensor names."""
 
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: PartSpec          # None: the block has no feed-forward (arrangements that allow it)
     norm: PartSpec
     arrangement: str = "pre_norm"
     names: dict = field(default_factory=dict)
@@ -72,6 +72,9 @@ class LayerCall:
     layer: int
     cache: int
     writes_cache: bool = True
+    # operations on the residual stream that run right before this call, in order: pairs of
+    # (name of an entry of ``ModelSpec.stream_ops``, argument), e.g. the number of a pass
+    before: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -90,6 +93,15 @@ class ModelSpec:
     # a position encoding that adds to the embeddings before the first block (learned or
     # absolute positions); None: positions enter inside the mixers only
     embedding_position: PartSpec = None
+    # logits <- cap * tanh(logits / cap); 0: none
+    logit_softcap: float = 0.0
+    # operations on the residual stream between blocks, by name: ((name, PartSpec), ...); a
+    # ``LayerCall.before`` says where one runs.  Its tensors live under "{prefix}{name}"
+    stream_ops: tuple = ()
+    # (pattern, replacement) pairs applied in order, as regular-expression substitutions, to every
+    # checkpoint tensor name the parts ask for: a checkpoint that stores "x.q" where the parts say
+    # "x.q.weight" gives ((r"\.weight$", ""),)
+    name_rules: tuple = ()
 
     def name_of(self, key: str, **fmt) -> str:
         return self.names.get(key, MODEL_NAMES[key]).format(prefix=self.weight_prefix, **fmt)

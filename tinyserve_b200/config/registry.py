@@ -11,6 +11,7 @@ from __future__ import annotations
 import json
 import os
 
+from .dudatar import DudatarConfig
 from .model_config import ConfigError, ModelConfig, Qwen3Config
 
 ARCHITECTURES: dict[str, type] = {}
@@ -25,17 +26,28 @@ def register_architecture(name: str, config_cls: type) -> None:
 
 def architecture_of(raw: dict) -> str:
     names = raw.get("architectures")
+    if not names and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]           # some configurations name their one architecture plainly
     if not names or not isinstance(names, (list, tuple)):
         raise ConfigError("config.json has no 'architectures' list")
     return names[0]
 
 
-def config_from_dict(raw: dict) -> ModelConfig:
+def config_from_dict(raw: dict, model_dir: str = "") -> ModelConfig:
+    """``model_dir``: the folder the configuration came from, for a configuration class that
+    takes sizes from the shapes of the checkpoint's tensors (``reads_tensor_shapes``)."""
     name = architecture_of(raw)
     if name not in ARCHITECTURES:
         raise ConfigError(
             f"architecture {name!r} is not registered; known: {sorted(ARCHITECTURES)}")
-    return ARCHITECTURES[name].from_dict(raw)
+    cls = ARCHITECTURES[name]
+    if getattr(cls, "reads_tensor_shapes", False):
+        shapes = None
+        if model_dir and any(f.endswith(".safetensors") for f in os.listdir(model_dir)):
+            from ..weights.loader import tensor_shapes
+            shapes = tensor_shapes(model_dir)
+        return cls.from_dict(raw, shapes)
+    return cls.from_dict(raw)
 
 
 def load_model_config(model_dir: str) -> ModelConfig:
@@ -43,7 +55,8 @@ def load_model_config(model_dir: str) -> ModelConfig:
     if not os.path.isfile(path):
         raise ConfigError(f"{model_dir!r} holds no config.json")
     with open(path) as fh:
-        return config_from_dict(json.load(fh))
+        return config_from_dict(json.load(fh), model_dir)
 
 
 register_architecture(Qwen3Config.architecture, Qwen3Config)
+register_architecture(DudatarConfig.architecture, DudatarConfig)

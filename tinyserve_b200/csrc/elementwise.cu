@@ -1107,3 +1107,329 @@ TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, c
     return ts_fail("qk_norm_rope_kvwrite: unknown dtype %d", dtype);
   return 0;
 }
+
+// ------------------------------------------------------------------ (sum of addends +) LayerNorm
+// Row m of the 32-bit residual, plus up to two addends stored as T, is normalised as
+// (v - mean) / sqrt(var + eps) * weight (+ bias), var the mean of the squared deviations; with
+// `write_residual` the sum goes back to the residual.  With `rows` only those rows are read
+// (row i of the output is row rows[i] of the inputs).  The row waits in shared memory between
+// the passes (mean, deviations, output), so every element is loaded once.
+template <typename T>
+__global__ void add_layernorm_kernel(const T* __restrict__ x1, const T* __restrict__ x2, float* __restrict__ residual,
+                                     VecParam w, const void* __restrict__ bias, int bias_is_f32, float eps,
+                                     T* __restrict__ out, const int* __restrict__ rows, int n, int write_residual) {
+  extern __shared__ float ln_row[];
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t m = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* r = residual + m * n;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = r[c];
+    if (x1) v += to_f32<T>(x1[m * n + c]);
+    if (x2) v += to_f32<T>(x2[m * n + c]);
+    if (write_residual) r[c] = v;
+    ln_row[c] = v;
+    sum += v;
+  }
+  const float mean = block_sum(sum, scratch) / (float)n;
+  float dev = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float d = ln_row[c] - mean;
+    dev += d * d;
+  }
+  const float rstd = rsqrtf(block_sum(dev, scratch) / (float)n + eps);
+  VecParam b{bias, bias_is_f32};
+  T* o = out + (size_t)blockIdx.x * n;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = (ln_row[c] - mean) * rstd * w[c];
+    if (bias) v += b[c];
+    o[c] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+int launch_add_layernorm(const void* x1, const void* x2, float* residual, VecParam w, const void* bias, int bias_is_f32,
+                         float eps, void* out, const int* rows, int num_out_rows, int n, int write_residual,
+                         cudaStream_t stream) {
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  const size_t smem = (size_t)n * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return ts_fail("add_layernorm: a row of %d elements does not fit shared memory", n);
+  }
+  TS_LAUNCH("add_layernorm", add_layernorm_kernel<T>, num_out_rows, threads, smem, stream, (const T*)x1, (const T*)x2,
+            residual, w, bias, bias_is_f32, eps, (T*)out, rows, n, write_residual);
+  return 0;
+}
+
+TS_EXPORT int ts_add_layernorm(int dtype, const void* x1, const void* x2, float* residual, const void* weight,
+                               int weight_is_f32, const void* bias, int bias_is_f32, float eps, void* out,
+                               const int* rows, int num_out_rows, int n, int write_residual, cudaStream_t stream) {
+  TS_REQUIRE(num_out_rows > 0 && n > 0 && residual && weight && out, "add_layernorm: empty input");
+  TS_REQUIRE((size_t)n * sizeof(float) <= 200 * 1024, "add_layernorm: rows of %d elements are too long", n);
+  VecParam w{weight, weight_is_f32};
+  if (dtype == TS_F32)
+    return launch_add_layernorm<float>(x1, x2, residual, w, bias, bias_is_f32, eps, out, rows, num_out_rows, n, write_residual, stream);
+  if (dtype == TS_BF16)
+    return launch_add_layernorm<__nv_bfloat16>(x1, x2, residual, w, bias, bias_is_f32, eps, out, rows, num_out_rows, n, write_residual, stream);
+  return ts_fail("add_layernorm: unknown dtype %d", dtype);
+}
+
+// ------------------------------------------------------------------ sum of two tensors stored as T
+template <typename T>
+__global__ void sum2_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t count) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(to_f32<T>(a[i]) + to_f32<T>(b[i]));
+}
+
+TS_EXPORT int ts_sum2(int dtype, const void* a, const void* b, void* out, long long count, cudaStream_t stream) {
+  TS_REQUIRE(count > 0, "sum2: empty input");
+  const int blocks = (int)((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
+  if (dtype == TS_F32) TS_LAUNCH("sum2", sum2_kernel<float>, blocks, 256, 0, stream, (const float*)a, (const float*)b, (float*)out, (size_t)count);
+  else if (dtype == TS_BF16) TS_LAUNCH("sum2", sum2_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, (size_t)count);
+  else return ts_fail("sum2: unknown dtype %d", dtype);
+  return 0;
+}
+
+// ------------------------------------------------------------------ soft cap of logits
+// x <- cap * tanh(x / cap), in place, 32-bit
+__global__ void softcap_kernel(float* __restrict__ x, size_t count, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  const float inv = 1.f / cap;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv);
+}
+
+TS_EXPORT int ts_softcap(float* x, long long count, float cap, cudaStream_t stream) {
+  TS_REQUIRE(count > 0 && cap > 0.f, "softcap: empty input or a cap that is not positive");
+  const int blocks = (int)((count + 255) / 256 < 8192 ? (count + 255) / 256 : 8192);
+  TS_LAUNCH("softcap", softcap_kernel, blocks, 256, 0, stream, x, (size_t)count, cap);
+  return 0;
+}
+
+// ------------------------------------------------------------------ a vector added to every row (32-bit rows)
+__global__ void add_row_vector_kernel(float* __restrict__ x, VecParam v, int n) {
+  pdl_trigger();
+  pdl_wait();
+  float* r = x + (size_t)blockIdx.x * n;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) r[c] += v[c];
+}
+
+TS_EXPORT int ts_add_row_vector(float* x, const void* vec, int vec_is_f32, int num_rows, int n, cudaStream_t stream) {
+  TS_REQUIRE(num_rows > 0 && n > 0, "add_row_vector: empty input");
+  VecParam v{vec, vec_is_f32};
+  TS_LAUNCH("add_row_vector", add_row_vector_kernel, num_rows, n >= 512 ? 256 : 128, 0, stream, x, v, n);
+  return 0;
+}
+
+// ------------------------------------------------------------------ [residual + addends | first] as T
+// out [rows, 2 n]: columns [0, n) = residual + x1 + x2 (the stream as it stands, addends that
+// are still pending included), columns [n, 2 n) = `first` (the stream as it left the embedding):
+// the input of a product that re-injects the embedding into the stream.
+template <typename T>
+__global__ void stream_concat_kernel(const float* __restrict__ residual, const T* __restrict__ x1,
+                                     const T* __restrict__ x2, const float* __restrict__ first, T* __restrict__ out, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = residual[m * n + c];
+    if (x1) v += to_f32<T>(x1[m * n + c]);
+    if (x2) v += to_f32<T>(x2[m * n + c]);
+    out[m * 2 * n + c] = from_f32<T>(v);
+    out[m * 2 * n + n + c] = from_f32<T>(first[m * n + c]);
+  }
+}
+
+TS_EXPORT int ts_stream_concat(int dtype, const float* residual, const void* x1, const void* x2, const float* first,
+                               void* out, int num_rows, int n, cudaStream_t stream) {
+  TS_REQUIRE(num_rows > 0 && n > 0, "stream_concat: empty input");
+  const int threads = n >= 512 ? 256 : 128;
+  if (dtype == TS_F32) TS_LAUNCH("stream_concat", stream_concat_kernel<float>, num_rows, threads, 0, stream, residual, (const float*)x1, (const float*)x2, first, (float*)out, n);
+  else if (dtype == TS_BF16) TS_LAUNCH("stream_concat", stream_concat_kernel<__nv_bfloat16>, num_rows, threads, 0, stream, residual, (const __nv_bfloat16*)x1, (const __nv_bfloat16*)x2, first, (__nv_bfloat16*)out, n);
+  else return ts_fail("stream_concat: unknown dtype %d", dtype);
+  return 0;
+}
+
+// ------------------------------------------------------------------ mean of RMS-normed branches
+// out[m, :] = (1 / count) * sum_i x_i[m, :] * rsqrt(mean(x_i[m, :]^2) + eps) * w_i: the outputs of
+// mixers that run side by side, each normalised over the model width with a weight of its own.
+constexpr int MAX_BRANCHES = 4;
+struct Branches {
+  const void* x[MAX_BRANCHES];
+  const void* w[MAX_BRANCHES];
+  int count, w_is_f32;
+};
+
+template <typename T>
+__global__ void mean_of_normed_kernel(Branches br, float eps, T* __restrict__ out, int n) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  float rstd[MAX_BRANCHES];
+#pragma unroll
+  for (int i = 0; i < MAX_BRANCHES; ++i) {
+    rstd[i] = 0.f;
+    if (i < br.count) {
+      const T* x = static_cast<const T*>(br.x[i]) + m * n;
+      float acc = 0.f;
+      for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float v = to_f32<T>(x[c]);
+        acc += v * v;
+      }
+      rstd[i] = rsqrtf(block_sum(acc, scratch) / (float)n + eps);
+    }
+  }
+  const float share = 1.f / (float)br.count;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_BRANCHES; ++i)
+      if (i < br.count) {
+        VecParam w{br.w[i], br.w_is_f32};
+        v += to_f32<T>(static_cast<const T*>(br.x[i])[m * n + c]) * rstd[i] * w[c];
+      }
+    out[m * n + c] = from_f32<T>(v * share);
+  }
+}
+
+TS_EXPORT int ts_mean_of_normed(int dtype, int count, const void* const* xs, const void* const* ws, int w_is_f32,
+                                float eps, void* out, int num_rows, int n, cudaStream_t stream) {
+  TS_REQUIRE(num_rows > 0 && n > 0, "mean_of_normed: empty input");
+  TS_REQUIRE(count >= 1 && count <= MAX_BRANCHES, "mean_of_normed: 1 to %d branches, got %d", MAX_BRANCHES, count);
+  Branches br{};
+  br.count = count;
+  br.w_is_f32 = w_is_f32;
+  for (int i = 0; i < count; ++i) { br.x[i] = xs[i]; br.w[i] = ws[i]; }
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  if (dtype == TS_F32) TS_LAUNCH("mean_of_normed", mean_of_normed_kernel<float>, num_rows, threads, 0, stream, br, eps, (float*)out, n);
+  else if (dtype == TS_BF16) TS_LAUNCH("mean_of_normed", mean_of_normed_kernel<__nv_bfloat16>, num_rows, threads, 0, stream, br, eps, (__nv_bfloat16*)out, n);
+  else return ts_fail("mean_of_normed: unknown dtype %d", dtype);
+  return 0;
+}
+
+// ------------------------------------------------------------------ rotary + unit norm + padded cache write
+// q [T, H * dim], k [T, G * dim], v [T, G * vdim] with row strides of their own (they may be
+// column ranges of one projection).  One warp per (token, head):
+//   q and k heads: rotary on the first rotary_dim elements, then (with `unit_norm`) division by
+//   the head's root mean square over dim (eps inside the root, no weight), then stored with D
+//   elements per head, [dim, D) zero: q to q_out [T, H, D], k to the key page of the token's slot;
+//   v heads: copied to the value page, [vdim, D) zero.
+// D >= max(dim, vdim) is the head size of the attention kernel: zero key columns add nothing to
+// a score and zero value columns give output columns that the caller drops.
+template <typename T>
+__global__ void rope_unit_kvwrite_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk,
+                                         const T* __restrict__ v, long long ldv, T* __restrict__ q_out,
+                                         const int* __restrict__ positions, RopeArgs rope, int unit_norm, float eps,
+                                         int H, int G, int dim, int vdim, int D, T* __restrict__ k_cache,
+                                         T* __restrict__ v_cache, const int* __restrict__ slot_mapping, int page_size,
+                                         int heads_total) {
+  pdl_trigger();
+  pdl_wait();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int R = rope.rotary_dim, half = R >> 1;
+  for (int head = blockIdx.y * warps + warp; head < heads_total; head += gridDim.y * warps) {
+    const T* src;
+    T* dst;
+    bool is_v = false;
+    if (head < H) {
+      src = q + (size_t)t * ldq + (size_t)head * dim;
+      dst = q_out + ((size_t)t * H + head) * D;
+    } else {
+      const int slot = slot_mapping[t];
+      if (slot < 0) continue;
+      is_v = head >= H + G;
+      const int g = is_v ? head - H - G : head - H;
+      const size_t page = slot / page_size, in_page = slot % page_size;
+      src = is_v ? v + (size_t)t * ldv + (size_t)g * vdim : k + (size_t)t * ldk + (size_t)g * dim;
+      dst = (is_v ? v_cache : k_cache) + ((page * G + g) * page_size + in_page) * D;
+    }
+    if (is_v) {
+      for (int i = lane; i < D; i += 32) dst[i] = i < vdim ? src[i] : from_f32<T>(0.f);
+      continue;
+    }
+    const int pos = positions[t];
+    auto rotated = [&](int i) {
+      const float a = to_f32<T>(src[i]);
+      if (i >= R) return a;
+      const int j = rope.interleaved ? i >> 1 : (i < half ? i : i - half);
+      const bool first = rope.interleaved ? !(i & 1) : i < half;
+      const int mate = rope.interleaved ? i ^ 1 : (first ? i + half : i - half);
+      const float b = to_f32<T>(src[mate]);
+      const float c = rope.cos[(size_t)pos * half + j], s = rope.sin[(size_t)pos * half + j];
+      return first ? a * c - b * s : a * c + b * s;
+    };
+    float rstd = 1.f;
+    if (unit_norm) {
+      float acc = 0.f;
+      for (int i = lane; i < dim; i += 32) {
+        const float r = rotated(i);
+        acc += r * r;
+      }
+      rstd = rsqrtf(warp_sum(acc) / (float)dim + eps);
+    }
+    for (int i = lane; i < D; i += 32) dst[i] = from_f32<T>(i < dim ? rotated(i) * rstd : 0.f);
+  }
+}
+
+TS_EXPORT int ts_rope_unit_kvwrite(int dtype, const void* q, long long ldq, const void* k, long long ldk, const void* v,
+                                   long long ldv, void* q_out, const int* positions, const float* cos, const float* sin,
+                                   int rotary_dim, int interleaved, int unit_norm, float eps, int num_tokens, int H, int G,
+                                   int dim, int vdim, int D, void* k_cache, void* v_cache, const int* slot_mapping,
+                                   int page_size, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && H > 0 && G > 0 && dim > 0 && vdim > 0 && D >= dim && D >= vdim,
+             "rope_unit_kvwrite: sizes do not fit (dim %d, vdim %d, stored head size %d)", dim, vdim, D);
+  TS_REQUIRE(rotary_dim >= 0 && rotary_dim <= dim && rotary_dim % 2 == 0,
+             "rope_unit_kvwrite: rotary_dim %d does not fit head size %d", rotary_dim, dim);
+  TS_REQUIRE(rotary_dim == 0 || (cos && sin), "rope_unit_kvwrite: rotary without tables");
+  TS_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && page_size > 0), "rope_unit_kvwrite: cache write without a cache");
+  const int heads_total = slot_mapping ? H + 2 * G : H;
+  const int warps = num_tokens >= 256 ? 8 : 4;
+  dim3 grid(num_tokens, num_tokens >= 256 ? 1 : (heads_total + warps - 1) / warps);
+  RopeArgs rope{cos, sin, rotary_dim, interleaved};
+  if (dtype == TS_F32)
+    TS_LAUNCH("rope_unit_kvwrite", rope_unit_kvwrite_kernel<float>, grid, warps * 32, 0, stream, (const float*)q, ldq,
+              (const float*)k, ldk, (const float*)v, ldv, (float*)q_out, positions, rope, unit_norm, eps, H, G, dim, vdim, D,
+              (float*)k_cache, (float*)v_cache, slot_mapping, page_size, heads_total);
+  else if (dtype == TS_BF16)
+    TS_LAUNCH("rope_unit_kvwrite", rope_unit_kvwrite_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream,
+              (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv,
+              (__nv_bfloat16*)q_out, positions, rope, unit_norm, eps, H, G, dim, vdim, D, (__nv_bfloat16*)k_cache,
+              (__nv_bfloat16*)v_cache, slot_mapping, page_size, heads_total);
+  else
+    return ts_fail("rope_unit_kvwrite: unknown dtype %d", dtype);
+  return 0;
+}
+
+// ------------------------------------------------------------------ one sigmoid gate per head
+// out [T, H * vdim] = attn [T, H, D][..., :vdim] * sigmoid(gate[t * ldg + h])
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ attn, const T* __restrict__ gate, long long ldg,
+                                 T* __restrict__ out, int H, int D, int vdim) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < H * vdim; i += blockDim.x) {
+    const int h = i / vdim, c = i % vdim;
+    float v = to_f32<T>(attn[(t * H + h) * D + c]);
+    if (gate) v *= 1.f / (1.f + expf(-to_f32<T>(gate[t * ldg + h])));
+    out[t * H * vdim + i] = from_f32<T>(v);
+  }
+}
+
+TS_EXPORT int ts_head_gate(int dtype, const void* attn, const void* gate, long long ldg, void* out, int num_tokens, int H,
+                           int D, int vdim, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && H > 0 && vdim > 0 && D >= vdim, "head_gate: sizes do not fit");
+  const int threads = H * vdim >= 512 ? 256 : 128;
+  if (dtype == TS_F32) TS_LAUNCH("head_gate", head_gate_kernel<float>, num_tokens, threads, 0, stream, (const float*)attn, (const float*)gate, ldg, (float*)out, H, D, vdim);
+  else if (dtype == TS_BF16) TS_LAUNCH("head_gate", head_gate_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, H, D, vdim);
+  else return ts_fail("head_gate: unknown dtype %d", dtype);
+  return 0;
+}

@@ -19,7 +19,7 @@ import os
 import sys
 
 DEFAULT_PAGE_SIZE = 16
-DEFAULT_MAX_LIVE = 8
+DEFAULT_MAX_LIVE = 4
 ROUND_TOKENS = 64
 
 

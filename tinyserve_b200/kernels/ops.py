@@ -192,8 +192,8 @@ _NO_SCALE = (c_void_p(0), c_int(0), c_float(0.0))
 
 
 def materialize(x):
-    """An ordinary tensor from what a product or a norm returned."""
-    return x.materialize() if isinstance(x, (SplitPartials, PendingProduct, ScaledRows)) else x
+    """An ordinary tensor from what a product, a norm or a block returned."""
+    return x.materialize() if isinstance(x, (SplitPartials, PendingProduct, ScaledRows, PairSum)) else x
 
 
 def launch_count() -> int:
@@ -1009,9 +1009,11 @@ def linear(x, weight, bias=None, out_float32=False, allow_partials=False, allow_
         x = scale.materialize()
     if x.dtype == torch.bfloat16:
         # a plain library product (and its bias epilogue), as in tinyserve
+        if bias is not None and out_float32:
+            # the sum stays 32-bit: the library's product, then this package's add of the bias
+            return add_row_vector_(torch.mm(x, weight.t(), out_dtype=torch.float32), bias)
         if bias is not None:
-            out = torch.addmm(bias.to(torch.bfloat16), x, weight.t())
-            return out.float() if out_float32 else out
+            return torch.addmm(bias.to(torch.bfloat16), x, weight.t())
         if out_float32:
             return torch.mm(x, weight.t(), out_dtype=torch.float32)
         return torch.mm(x, weight.t())
@@ -1064,3 +1066,201 @@ def apply_repetition_penalty(logits, rows, ids, penalty):
         _ptr(logits), c_longlong(logits.stride(0)), c_int(logits.shape[1]), _ptr(rows), _ptr(ids),
         c_int(rows.shape[0]), c_int(ids.shape[1]), _ptr(penalty), _stream()))
     return logits
+
+
+# ----------------------------------------------------------------------------- parallel blocks, layer norm, soft cap
+class PairSum:
+    """The outputs of two sub-layers that read the same input and are summed into the stream
+    (a block that runs its mixer and its feed-forward side by side).  The kernel of the next
+    norm, or of the next product on the stream, adds both to the 32-bit residual while it loads,
+    so the sum is never rounded to the compute dtype; ``materialize()`` adds them for any other
+    consumer.  ``b`` may be None."""
+
+    def __init__(self, a, b=None):
+        self.a, self.b = materialize(a), materialize(b)
+        self.shape, self.dtype, self.device = tuple(self.a.shape), self.a.dtype, self.a.device
+
+    def materialize(self):
+        if self.b is None:
+            return self.a
+        out = torch.empty_like(self.a)
+        lib = _elementwise()
+        _check(lib, lib.ts_sum2(c_int(_dt(self.a)), _ptr(self.a), _ptr(self.b), _ptr(out), c_longlong(self.a.numel()),
+                                _stream()))
+        return out
+
+
+def _addends(x):
+    if x is None:
+        return None, None
+    if isinstance(x, PairSum):
+        return x.a, x.b
+    return materialize(x), None
+
+
+def add_layernorm(x, residual, weight, eps, out_dtype, bias=None, rows=None):
+    """residual (float32, in place) += x; returns (residual - mean) / sqrt(var + eps) * weight
+    (+ bias) as ``out_dtype``, var the mean of the squared deviations.  ``x``: None, a tensor of
+    the compute dtype or a PairSum.  With ``rows`` (int32) only those rows are normalised and
+    returned, and the residual is left as it is."""
+    x1, x2 = _addends(x)
+    _cuda(x1, x2, residual, weight, bias, rows)
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise TypeError("the residual stream is contiguous float32")
+    for a in (x1, x2):
+        if a is not None and (a.dtype != out_dtype or not a.is_contiguous() or a.shape != residual.shape):
+            raise TypeError("add_layernorm: addends are contiguous, of the compute dtype and of the residual's shape")
+    n = residual.shape[1]
+    num_out = residual.shape[0] if rows is None else rows.shape[0]
+    out = torch.empty(num_out, n, dtype=out_dtype, device=residual.device)
+    lib = _elementwise()
+    _check(lib, lib.ts_add_layernorm(
+        c_int(_DTYPE[out_dtype]), _ptr(x1), _ptr(x2), _ptr(residual), _ptr(weight), c_int(_vec_flag(weight, out_dtype)),
+        _ptr(bias), c_int(_vec_flag(bias, out_dtype) if bias is not None else 0), c_float(eps), _ptr(out), _ptr(rows),
+        c_int(num_out), c_int(n), c_int(0 if rows is not None else 1), _stream()))
+    return out
+
+
+def softcap_(logits, cap):
+    """logits (float32, in place) <- cap * tanh(logits / cap)."""
+    _cuda(logits)
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise TypeError("softcap: logits are contiguous float32")
+    lib = _elementwise()
+    _check(lib, lib.ts_softcap(_ptr(logits), c_longlong(logits.numel()), c_float(cap), _stream()))
+    return logits
+
+
+def add_row_vector_(x, vec):
+    """x (float32 [rows, n], in place) += vec [n]."""
+    _cuda(x, vec)
+    if x.dtype != torch.float32 or not x.is_contiguous() or vec.shape[-1] != x.shape[1]:
+        raise TypeError("add_row_vector: contiguous float32 rows and a vector of their length")
+    lib = _elementwise()
+    _check(lib, lib.ts_add_row_vector(_ptr(x), _ptr(vec), c_int(_vec_flag(vec, torch.bfloat16)), c_int(x.shape[0]),
+                                      c_int(x.shape[1]), _stream()))
+    return x
+
+
+def stream_concat(residual, pending, first, out_dtype):
+    """[rows, 2 n] of ``out_dtype``: the stream as it stands (residual plus what is still pending:
+    None, a tensor or a PairSum) beside ``first`` (float32 [rows, n])."""
+    x1, x2 = _addends(pending)
+    _cuda(residual, x1, x2, first)
+    rows, n = residual.shape
+    out = torch.empty(rows, 2 * n, dtype=out_dtype, device=residual.device)
+    lib = _elementwise()
+    _check(lib, lib.ts_stream_concat(c_int(_DTYPE[out_dtype]), _ptr(residual), _ptr(x1), _ptr(x2), _ptr(first), _ptr(out),
+                                     c_int(rows), c_int(n), _stream()))
+    return out
+
+
+def mean_of_normed(xs, weights, eps):
+    """mean over i of xs[i] * rsqrt(mean(xs[i]^2) + eps) * weights[i], row by row ([rows, n] each)."""
+    xs = [materialize(x) for x in xs]
+    _cuda(*xs, *weights)
+    if len({(tuple(x.shape), x.dtype) for x in xs}) != 1 or not all(x.is_contiguous() for x in xs):
+        raise TypeError("mean_of_normed: branches are contiguous and alike in shape and dtype")
+    if len({w.dtype for w in weights}) != 1:
+        raise TypeError("mean_of_normed: the branches' weights differ in dtype")
+    rows, n = xs[0].shape
+    out = torch.empty_like(xs[0])
+    count = len(xs)
+    xp = (c_void_p * count)(*[x.data_ptr() for x in xs])
+    wp = (c_void_p * count)(*[w.data_ptr() for w in weights])
+    lib = _elementwise()
+    _check(lib, lib.ts_mean_of_normed(c_int(_dt(xs[0])), c_int(count), xp, wp, c_int(_vec_flag(weights[0], xs[0].dtype)),
+                                      c_float(eps), _ptr(out), c_int(rows), c_int(n), _stream()))
+    return out
+
+
+def _columns(t):
+    """(pointer, row stride) of a 2-d tensor or a column range of one."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError("operand must be a 2-d tensor, contiguous along its rows")
+    return _ptr(t), c_longlong(t.stride(0))
+
+
+def rope_unit_kvwrite(q, k, v, positions, num_heads, num_kv_heads, dim, vdim, stored_dim, rotary=None,
+                      unit_norm=False, eps=0.0, k_cache=None, v_cache=None, slot_mapping=None, page_size=0):
+    """Rotary encoding of q and k (first ``rotary.rotary_dim`` elements of every head), then, with
+    ``unit_norm``, division of every head of q and k by its root mean square over ``dim``; q goes
+    to a [T, H, stored_dim] tensor (returned), k and v to the cache slots of ``slot_mapping``
+    (None: nothing is written), heads padded with zeros to ``stored_dim``.  q [T, H dim],
+    k [T, Hkv dim], v [T, Hkv vdim] may be column ranges of one projection."""
+    _cuda(q, k, v, positions, k_cache, v_cache, slot_mapping)
+    T = q.shape[0]
+    if q.shape[1] != num_heads * dim or k.shape[1] != num_kv_heads * dim or v.shape[1] != num_kv_heads * vdim:
+        raise ValueError("rope_unit_kvwrite: q, k, v do not have heads x size columns")
+    if k_cache is not None and (k_cache.dtype != q.dtype or k_cache.shape[-1] != stored_dim or not k_cache.is_contiguous()
+                                or not v_cache.is_contiguous()):
+        raise TypeError("rope_unit_kvwrite: the cache does not fit the activations")
+    out = torch.empty(T, num_heads, stored_dim, dtype=q.dtype, device=q.device)
+    cos = rotary.cos if rotary is not None else None
+    sin = rotary.sin if rotary is not None else None
+    lib = _elementwise()
+    _check(lib, lib.ts_rope_unit_kvwrite(
+        c_int(_dt(q)), *_columns(q), *_columns(k), *_columns(v), _ptr(out), _ptr(positions), _ptr(cos), _ptr(sin),
+        c_int(rotary.rotary_dim if rotary is not None else 0), c_int(int(rotary.interleaved) if rotary is not None else 0),
+        c_int(1 if unit_norm else 0), c_float(eps), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(dim),
+        c_int(vdim), c_int(stored_dim), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), c_int(page_size), _stream()))
+    return out
+
+
+def head_gate(attn, gate, vdim):
+    """[T, H * vdim] = attn [T, H, D][..., :vdim] * sigmoid(gate [T, H]); ``gate`` None: the
+    columns are only gathered."""
+    _cuda(attn, gate)
+    T, H, D = attn.shape
+    if not attn.is_contiguous():
+        raise ValueError("head_gate: attn must be contiguous")
+    out = torch.empty(T, H * vdim, dtype=attn.dtype, device=attn.device)
+    gp, ld = _columns(gate) if gate is not None else (c_void_p(0), c_longlong(0))
+    lib = _elementwise()
+    _check(lib, lib.ts_head_gate(c_int(_dt(attn)), _ptr(attn), gp, ld, _ptr(out), c_int(T), c_int(H), c_int(D),
+                                 c_int(vdim), _stream()))
+    return out
+
+
+# ----------------------------------------------------------------------------- linear attention with a matrix state
+LINEAR_ATTENTION_MAX_VALUE_DIM = 256
+
+
+def _linear_attention(key_dim: int):
+    if key_dim % 4 or not 4 <= key_dim <= 512:
+        raise ValueError(f"key size {key_dim} is not supported: linear attention takes multiples of 4 up to 512")
+    return build.load_unit("linear_attention.cu", {"TS_KEY_DIM": key_dim})
+
+
+def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, out_dtype, *, decay=None,
+                     decay_logits=None, tau=1.0, rotary=None, q_scale=1.0, k_scale=1.0, norm_weight=None, eps=0.0):
+    """Per request and head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over this step's
+    tokens, from and to ``state`` [slots, H, key_dim, value_dim] (float32) at the requests' state
+    slots (``ctx.state_slots``, ``ctx.fresh``, ``ctx.cu_q``); returns [T, H * value_dim] =
+    o / rms(o) (* norm_weight) * silu(gate).  a_t: ``decay`` float32 [H] (one constant per head)
+    or ``decay_logits`` float32 [T, H * key_dim] with a = sigmoid(z)^(1 / tau).  q, k [T, H key_dim],
+    v, gate [T, H value_dim] may be column ranges of one projection.  ``rotary``: positions on q
+    and k; ``q_scale`` / ``k_scale``: constant factors (after the rotation)."""
+    _cuda(q, k, v, gate, state, decay, decay_logits, norm_weight)
+    T = q.shape[0]
+    H = num_heads
+    if q.shape[1] != H * key_dim or k.shape[1] != H * key_dim or v.shape[1] != H * value_dim:
+        raise ValueError("linear_attention: q, k, v do not have heads x size columns")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, key_dim, value_dim) or not state.is_contiguous():
+        raise TypeError("linear_attention: the state is contiguous float32 [slots, H, key_dim, value_dim]")
+    if (decay is None) == (decay_logits is None):
+        raise ValueError("linear_attention: either per-head decays or per-channel logits")
+    if decay_logits is not None and (decay_logits.dtype != torch.float32 or decay_logits.shape[1] != H * key_dim):
+        raise TypeError("linear_attention: decay logits are float32 [T, H * key_dim]")
+    out = torch.empty(T, H * value_dim, dtype=out_dtype, device=q.device)
+    zp, zld = _columns(decay_logits) if decay_logits is not None else (c_void_p(0), c_longlong(0))
+    gp, gld = _columns(gate) if gate is not None else (c_void_p(0), c_longlong(0))
+    lib = _linear_attention(key_dim)
+    _check(lib, lib.ts_linear_attention(
+        c_int(_dt(q)), *_columns(q), *_columns(k), *_columns(v), gp, gld, zp, zld, c_float(tau), _ptr(decay),
+        _ptr(ctx.positions), _ptr(rotary.cos if rotary is not None else None),
+        _ptr(rotary.sin if rotary is not None else None), c_int(rotary.rotary_dim if rotary is not None else 0),
+        c_float(q_scale), c_float(k_scale), _ptr(state), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(ctx.cu_q),
+        c_int(ctx.num_requests), _ptr(norm_weight), c_int(_vec_flag(norm_weight, out_dtype) if norm_weight is not None else 0),
+        c_float(eps), _ptr(out), c_longlong(out.stride(0)), c_int(H), c_int(value_dim), _stream()))
+    return out

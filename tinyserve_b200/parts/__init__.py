@@ -1,10 +1,13 @@
 from .base import (CacheSpec, CacheTensor, FeedForward, Mixer, Norm, ParamSpec, Part, PositionEncoding, Source,
-                   StateSpec, build_feed_forward, build_mixer, build_norm,
+                   StateSpec, StreamOp, build_feed_forward, build_mixer, build_norm,
                    build_position_encoding, register_feed_forward, register_mixer, register_norm,
-                   register_position_encoding)
-from .norm import RMSNorm
+                   register_position_encoding, register_stream_op)
+from .norm import LayerNorm, RMSNorm
 from .rotary import Rotary
 from .attention import Attention
 from .mlp import GatedMLP
-from .block import ARRANGEMENTS, PreNormBlock, build_block
+from .linear_attention import GatedLinearAttention, Retention
+from .side_by_side import SideBySide
+from .stream import InputInjection
+from .block import ARRANGEMENTS, ParallelBlock, PreNormBlock, build_block
 from .model import BoundCall, DecoderModel, Embedding, LMHead, build_model

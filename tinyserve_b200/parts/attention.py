@@ -6,7 +6,15 @@ keys and values written to the cache pages of this step's tokens (serve.py:897-9
 attention of every query over its request's cached keys with j <= position and,
 with ``window`` > 0, j > position - window (serve.py:668-680), output projection
 (serve.py:883).  All sizes are parameters, and so are the checkpoint's names of the four
-projections and the two norms (``names``)."""
+projections and the two norms (``names``).
+
+Beyond that model: values may have a head size of their own (``value_dim``); q and k may be
+divided by their root mean square per head, without a weight, after the position encoding
+(``unit_norm_eps``); every head's output may be multiplied by sigmoid of one number per head, a
+projection of the same input (``head_gate``, rows of the fused projection after v).  With any
+of these the heads are stored ``stored_dim`` wide (the larger of the two head sizes, rounded up
+to what the attention kernels take), padded with zeros: zero key columns add nothing to a score
+and the padded output columns are dropped."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -14,7 +22,8 @@ from .base import (CacheSpec, Mixer, ParamSpec, Source, build_norm, build_positi
                    register_mixer)
 
 
-DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm"}
+DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm",
+                 "gate": "g_proj"}
 
 
 class Attention(Mixer):
@@ -22,7 +31,8 @@ class Attention(Mixer):
     capturable = True
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, bias=False, qk_norm=None,
-                 position=None, window=0, scale=None, names=None):
+                 position=None, window=0, scale=None, names=None, value_dim=None, unit_norm_eps=None,
+                 head_gate=False):
         super().__init__()
         self.names = dict(DEFAULT_NAMES, **(names or {}))
         if num_heads % num_kv_heads:
@@ -33,8 +43,21 @@ class Attention(Mixer):
         self.q_norm = build_norm(qk_norm, head_dim) if qk_norm is not None else None
         self.k_norm = build_norm(qk_norm, head_dim) if qk_norm is not None else None
         self.position = build_position_encoding(position) if position is not None else None
+        self.value_dim = int(value_dim) if value_dim else head_dim
+        self.unit_norm_eps = None if unit_norm_eps is None else float(unit_norm_eps)
+        self.head_gate = bool(head_gate)
+        #: the plain form runs the kernels that fuse per-head norm, rotary and cache write (and, for
+        #: a few decoded tokens, the attention itself); the general form has kernels of its own
+        self.general = self.value_dim != head_dim or self.unit_norm_eps is not None or self.head_gate
+        if self.general and (qk_norm is not None or bias):
+            raise ValueError("attention: a value size of its own, the unit norm and the head gate come "
+                             "without a weighted q/k norm and without biases")
+        widest = max(head_dim, self.value_dim)
+        self.stored_dim = -(-widest // 16) * 16 if self.general else head_dim
         self.q_size = num_heads * head_dim
         self.kv_size = num_kv_heads * head_dim
+        self.v_size = num_kv_heads * self.value_dim
+        self.gate_size = num_heads if self.head_gate else 0
 
     def children(self):
         out = {}
@@ -45,13 +68,16 @@ class Attention(Mixer):
         return out
 
     def param_specs(self):
-        q, kv = self.q_size, self.kv_size
+        q, kv, vs = self.q_size, self.kv_size, self.v_size
         nm = self.names
-        rows = ((nm["q"], 0, q), (nm["k"], q, q + kv), (nm["v"], q + kv, q + 2 * kv))
+        rows = ((nm["q"], 0, q), (nm["k"], q, q + kv), (nm["v"], q + kv, q + kv + vs))
+        if self.head_gate:
+            rows += ((nm["gate"], q + kv + vs, q + kv + vs + self.gate_size),)
         specs = {
-            "qkv_proj.weight": ParamSpec((q + 2 * kv, self.hidden_size), sources=tuple(
+            "qkv_proj.weight": ParamSpec((q + kv + vs + self.gate_size, self.hidden_size), sources=tuple(
                 Source(f"{n}.weight", a, b) for n, a, b in rows)),
-            "o_proj.weight": ParamSpec((self.hidden_size, q), sources=(Source(f"{nm['o']}.weight", 0, self.hidden_size),)),
+            "o_proj.weight": ParamSpec((self.hidden_size, self.num_heads * self.value_dim),
+                                       sources=(Source(f"{nm['o']}.weight", 0, self.hidden_size),)),
         }
         if self.bias:
             # drawn like a matrix in the random-weights mode: a bias of zeros would hide a fault
@@ -61,14 +87,34 @@ class Attention(Mixer):
 
     def cache_spec(self):
         kind = "window" if self.window > 0 else "full"
-        return CacheSpec(kind, self.num_kv_heads, self.head_dim, self.window)
+        return CacheSpec(kind, self.num_kv_heads, self.stored_dim, self.window)
 
     accepts_scaled_rows = True
 
     def work_tile_queries(self, dtype, page_size):
-        return ops.prefill_tile_queries(dtype, self.num_heads, self.num_kv_heads, self.head_dim, page_size)
+        return ops.prefill_tile_queries(dtype, self.num_heads, self.num_kv_heads, self.stored_dim, page_size)
+
+    def _forward_general(self, h, ctx, call):
+        qkv = ops.materialize(ops.linear(h, self.w["qkv_proj.weight"]))
+        q_end, k_end = self.q_size, self.q_size + self.kv_size
+        v_end = k_end + self.v_size
+        cache = ctx.cache(call.cache)
+        view = ctx.group(cache.group)
+        q = ops.rope_unit_kvwrite(
+            qkv[:, :q_end], qkv[:, q_end:k_end], qkv[:, k_end:v_end], ctx.positions, self.num_heads,
+            self.num_kv_heads, self.head_dim, self.value_dim, self.stored_dim, rotary=self.position,
+            unit_norm=self.unit_norm_eps is not None, eps=self.unit_norm_eps or 0.0, k_cache=cache.k, v_cache=cache.v,
+            slot_mapping=view.slot_mapping if call.writes_cache else None, page_size=view.page_size)
+        out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window)
+        if self.head_gate or self.stored_dim != self.value_dim:
+            out = ops.head_gate(out, qkv[:, v_end:] if self.head_gate else None, self.value_dim)
+        else:
+            out = out.view(out.shape[0], self.num_heads * self.value_dim)
+        return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
 
     def forward(self, h, ctx, call):
+        if self.general:
+            return self._forward_general(h, ctx, call)
         qkv = ops.linear(h, self.w["qkv_proj.weight"], self.w.get("qkv_proj.bias"), allow_partials=True)
         cache = ctx.cache(call.cache)
         view = ctx.group(cache.group)

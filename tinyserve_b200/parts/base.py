@@ -148,6 +148,10 @@ class Norm(Part):
     def forward(self, x, out=None):
         raise NotImplementedError
 
+    #: ``add_forward`` takes x as the block before left it (an ``ops.PairSum`` included) and adds
+    #: it in its own kernel; otherwise it gets a finished tensor
+    takes_pending = False
+
     def add_forward(self, x, residual, rows=None):
         """residual (float32, in place) += x (a tensor of the compute dtype, or None); returns
         norm(residual) in the compute dtype.  With ``rows`` (int32) only those rows are normalised
@@ -202,7 +206,22 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamOp(Part):
+    """An operation on the residual stream between blocks (``ModelSpec.stream_ops``, placed by
+    ``LayerCall.before``).  ``needs_first``: the model keeps the stream as it left the embedding
+    (float32 [T, hidden]) and hands it over as ``first``."""
+
+    needs_first = False
+
+    def forward(self, residual, pending, first, ctx, arg):
+        """``residual`` float32 [T, hidden]; ``pending``: what the block before returned and the
+        stream has not taken in yet (None, a tensor or one of ops' unfinished sums).  Returns
+        (residual, pending) as the next block finds them."""
+        raise NotImplementedError
+
+
 MIXERS: dict[str, Callable] = {}
+STREAM_OPS: dict[str, Callable] = {}
 FEED_FORWARDS: dict[str, Callable] = {}
 NORMS: dict[str, Callable] = {}
 POSITION_ENCODINGS: dict[str, Callable] = {}
@@ -219,6 +238,7 @@ register_mixer = _register(MIXERS, "mixer")
 register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
+register_stream_op = _register(STREAM_OPS, "stream operation")
 
 
 def _build(table, what, spec: PartSpec, **extra):
@@ -241,3 +261,7 @@ def build_norm(spec: PartSpec, dim: int):
 
 def build_position_encoding(spec: PartSpec):
     return _build(POSITION_ENCODINGS, "position encoding", spec)
+
+
+def build_stream_op(spec: PartSpec):
+    return _build(STREAM_OPS, "stream operation", spec)

@@ -25,7 +25,7 @@ def add_and_norm(norm, x, residual, reader=None, rows=None, compute_dtype=None):
     finished tensor."""
     rms = norm.rms_parameters()
     if rms is None:
-        return norm.add_forward(ops.materialize(x), residual, rows=rows)
+        return norm.add_forward(x if norm.takes_pending else ops.materialize(x), residual, rows=rows)
     weight, eps = rms
     scaled_ok = rows is None and reader is not None and getattr(reader, "accepts_scaled_rows", False)
     return ops.add_rmsnorm(x, residual, weight, eps, compute_dtype or residual_compute_dtype(norm, x),
@@ -73,7 +73,36 @@ class PreNormBlock(Part):
         return self.ffn.forward(h, ctx)
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock}
+class ParallelBlock(Part):
+    """One norm, and the mixer and the feed-forward side by side on its output:
+    h = norm(r), r <- r + (mixer(h) + ffn(h)).  The block hands both outputs on as they are
+    (``ops.PairSum``); the kernel of the next norm adds them to the 32-bit residual, so their sum
+    is never rounded.  A layer without a feed-forward (``LayerSpec.ffn`` None) is r + mixer(h)."""
+    capturable = True
+
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        super().__init__()
+        self.mixer = build_mixer(spec.mixer)
+        self.ffn = build_feed_forward(spec.ffn) if spec.ffn is not None else None
+        self.input_norm = build_norm(spec.norm, hidden_size)
+        self._names = {"mixer": spec.name_of("mixer", self.mixer.tree_name),
+                       "ffn": spec.name_of("ffn", self.ffn.tree_name if self.ffn is not None else ""),
+                       "input_norm": spec.name_of("input_norm")}
+
+    def children(self):
+        n = self._names
+        out = {n["mixer"]: self.mixer, n["input_norm"]: self.input_norm}
+        if self.ffn is not None:
+            out[n["ffn"]] = self.ffn
+        return out
+
+    def forward(self, x, residual, ctx, call):
+        h = ops.materialize(add_and_norm(self.input_norm, x, residual, None, compute_dtype=ctx.dtype))
+        mixed = self.mixer.forward(h, ctx, call)
+        return ops.PairSum(mixed, self.ffn.forward(h, ctx) if self.ffn is not None else None)
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock}
 
 
 def build_block(spec: LayerSpec, hidden_size: int):

@@ -10,7 +10,7 @@ from dataclasses import dataclass
 
 from ..config.model_config import ModelConfig, ModelSpec
 from ..kernels import ops
-from .base import CacheSpec, ParamSpec, Part, StateSpec, build_norm, build_position_encoding
+from .base import CacheSpec, ParamSpec, Part, StateSpec, build_norm, build_position_encoding, build_stream_op
 from .block import add_and_norm, build_block
 
 
@@ -45,6 +45,7 @@ class BoundCall:
     cache: int
     state: int
     writes_cache: bool
+    before: tuple = ()      # (stream operation, argument) pairs that run right before the block
 
 
 @dataclass(frozen=True)
@@ -65,6 +66,9 @@ class DecoderModel(Part):
         self.lm_head = None if spec.tie_word_embeddings else LMHead(spec.vocab_size, spec.hidden_size)
         self.embed_position = (build_position_encoding(spec.embedding_position)
                                if spec.embedding_position is not None else None)
+        self.stream_ops = {name: build_stream_op(op) for name, op in spec.stream_ops}
+        for name, op in self.stream_ops.items():
+            op.set_path(f"{spec.weight_prefix}{name}")
         # checkpoint names are data of the specification
         self.embed_tokens.set_path(spec.name_of("embed"))
         for i, block in enumerate(self.blocks):
@@ -117,13 +121,16 @@ class DecoderModel(Part):
             if sspec is not None:
                 state_index = len(self.state_entries)
                 self.state_entries.append(sspec)
-            self.calls.append(BoundCall(call.layer, cache_index, state_index, call.writes_cache))
+            before = tuple((self.stream_ops[name], arg) for name, arg in call.before)
+            self.calls.append(BoundCall(call.layer, cache_index, state_index, call.writes_cache, before))
         self.group_sizes = group_sizes
 
     def named_parts(self):
         yield self.embed_tokens
         if self.embed_position is not None:
             yield from self.embed_position.named_parts()
+        for op in self.stream_ops.values():
+            yield from op.named_parts()
         for block in self.blocks:
             yield from block.named_parts()
         yield self.norm
@@ -140,14 +147,20 @@ class DecoderModel(Part):
         residual = ops.embed_lookup(self.embed_tokens.w["weight"], ctx.token_ids, ctx.slot_tokens)
         if self.embed_position is not None:
             self.embed_position.add_to_embeddings(residual, ctx)
+        first = residual.clone() if any(op.needs_first for op in self.stream_ops.values()) else None
         x = None
         for call in self.calls:
+            for op, arg in call.before:
+                residual, x = op.forward(residual, x, first, ctx, arg)
             x = self.blocks[call.layer].forward(x, residual, ctx, call)
         if ctx.num_logit_rows == 0:
             return None
         hidden = add_and_norm(self.norm, x, residual, rows=ctx.logit_rows, compute_dtype=ctx.dtype)
         head = self.lm_head.w["weight"] if self.lm_head is not None else self.embed_tokens.w["weight"]
-        return ops.linear(hidden, head, out_float32=True)
+        logits = ops.linear(hidden, head, out_float32=True)
+        if self.spec.logit_softcap > 0:
+            ops.softcap_(logits, self.spec.logit_softcap)
+        return logits
 
 
 def build_model(config: ModelConfig) -> DecoderModel:

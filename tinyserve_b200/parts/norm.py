@@ -34,3 +34,36 @@ class RMSNorm(Norm):
 
 
 register_norm("rmsnorm", RMSNorm)
+
+
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w (+ b), var the mean of the squared deviations, all in
+    32-bit, output in the compute dtype.  ``add_forward`` adds what the block before left (one or
+    two tensors) to the 32-bit residual in the same kernel."""
+    capturable = True
+    takes_pending = True
+
+    def __init__(self, dim: int, eps: float, bias: bool = False):
+        super().__init__()
+        self.dim, self.eps, self.bias = dim, float(eps), bool(bias)
+        self.compute_dtype = None
+
+    def prepare(self, runtime):
+        self.compute_dtype = runtime.dtype
+
+    def param_specs(self):
+        specs = {"weight": ParamSpec((self.dim,), role="vector", init="norm_weight")}
+        if self.bias:
+            specs["bias"] = ParamSpec((self.dim,), role="vector", init="normal")
+        return specs
+
+    def forward(self, x, out=None):
+        residual = x.float().contiguous()
+        return ops.add_layernorm(None, residual, self.w["weight"], self.eps, x.dtype, bias=self.w.get("bias"))
+
+    def add_forward(self, x, residual, rows=None):
+        return ops.add_layernorm(x, residual, self.w["weight"], self.eps, self.compute_dtype,
+                                 bias=self.w.get("bias"), rows=rows)
+
+
+register_norm("layernorm", LayerNorm)

@@ -1,0 +1,34 @@
+"""Operations on the residual stream between blocks.
+
+``InputInjection``: before pass t of a group of layers that runs several times with the same
+weights, the stream is mixed with the embedding output again, r <- W [r; r0] + step[t]
+(W [hidden, 2 hidden], the stream's columns first; step [times, hidden]).  The product takes
+[r; r0] in the compute dtype and leaves the new stream in 32-bit."""
+from __future__ import annotations
+
+from ..kernels import ops
+from .base import ParamSpec, StreamOp, register_stream_op
+
+
+class InputInjection(StreamOp):
+    capturable = True
+    needs_first = True
+
+    def __init__(self, hidden_size, times):
+        super().__init__()
+        self.hidden_size, self.times = hidden_size, int(times)
+
+    def param_specs(self):
+        return {"in.weight": ParamSpec((self.hidden_size, 2 * self.hidden_size)),
+                "step.weight": ParamSpec((self.times, self.hidden_size), role="vector", init="normal")}
+
+    def forward(self, residual, pending, first, ctx, arg):
+        if not 0 <= arg < self.times:
+            raise ValueError(f"input injection: pass {arg} of {self.times}")
+        both = ops.stream_concat(residual, pending, first, ctx.dtype)
+        mixed = ops.linear(both, self.w["in.weight"], out_float32=True)
+        ops.add_row_vector_(mixed, self.w["step.weight"][arg])
+        return mixed, None
+
+
+register_stream_op("input_injection", InputInjection)

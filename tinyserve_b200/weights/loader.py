@@ -16,6 +16,7 @@ as it has no home there either (serve.py:1385-1387)."""
 from __future__ import annotations
 
 import os
+import re
 from dataclasses import dataclass
 
 import torch
@@ -63,12 +64,15 @@ def _sources(local_name: str, spec: ParamSpec):
 def expected_tensors(model) -> list:
     """Every checkpoint tensor the model reads, in a fixed order."""
     out = []
+    rules = [(re.compile(pattern), repl) for pattern, repl in getattr(getattr(model, "spec", None), "name_rules", ())]
     for part in model.named_parts():
         for local, spec in part.param_specs().items():
             for src in _sources(local, spec):
                 shape = (src.row_end - src.row_start,) + tuple(spec.shape[1:])
-                out.append(ExpectedTensor(f"{part.path}.{src.name}", shape, part, local, spec,
-                                          src.row_start, src.row_end))
+                name = f"{part.path}.{src.name}" if part.path else src.name
+                for pattern, repl in rules:
+                    name = pattern.sub(repl, name)
+                out.append(ExpectedTensor(name, shape, part, local, spec, src.row_start, src.row_end))
     return out
 
 
@@ -78,6 +82,12 @@ def _param_dtype(spec: ParamSpec, engine_dtype, stored_dtypes):
     if spec.role == "vector" and all(d == torch.float32 for d in stored_dtypes):
         return torch.float32
     return engine_dtype
+
+
+def tensor_shapes(model_dir) -> dict:
+    """{tensor name: shape} of every ``*.safetensors`` file of the folder (headers only)."""
+    index, _ = _index_folder(model_dir)
+    return {name: shape for name, (_, shape, _) in index.items()}
 
 
 def _index_folder(model_dir):
