@@ -1,0 +1,380 @@
+"""Dudatar on the device against the plain implementation (tests/plain_dudatar.py): each
+mechanism alone through its kernel, then whole models through the step function: whole prompts,
+prompts against token-by-token decoding, portions down to two tokens, mixed batches with pages
+and state slots that are used again, far keys and long memories that the weights are made to
+show, the first tokens, long decoding, and greedy generation through the entry point."""
+import os
+
+import numpy as np
+import pytest
+import torch
+from safetensors.torch import load_file, save_file
+
+import plain_dudatar as plain
+from dudatar_configs import DUDATAR_TINY, dudatar_config, make_dudatar_dir
+from helpers import (collect_logits, lines_of, max_live_tokens, random_ids, schedule_mixed, schedule_portions,
+                     schedule_tail_decode, schedule_whole)
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+# Largest |logit difference|, and largest root-mean-square difference over the vocabulary at one
+# position, over the largest plain |logit|.  float32: 32-bit sums against float64; this is the
+# sharp test of every schedule.  bfloat16: products and activations rounded to 8 bits through
+# up to nine block runs of tiny random layers, whose unit norms and layer norms carry a rounding
+# of the small stream into the logits at full size; per configuration, about twice the largest
+# value measured on a B200 (X 2.4e-1, 6.4e-2; Y 4.8e-2, 1.8e-2; Z 9.8e-2, 3.1e-2; float32
+# 2.4e-5, 8.3e-6 at most), so it catches a kernel that is wrong, not one that rounds elsewhere.
+TOLERANCE = {"float32": 5e-5, "bfloat16": {"X": 4.5e-1, "Y": 1e-1, "Z": 2e-1}}
+RMS_TOLERANCE = {"float32": 1.7e-5, "bfloat16": {"X": 1.3e-1, "Y": 3.6e-2, "Z": 6.5e-2}}
+MEASURED = {}
+
+
+# ----------------------------------------------------------------------------- the step's batch, by hand
+class Batch:
+    """What a mechanism's kernel needs of a step: requests of given lengths, each from position
+    ``starts[b]``, with state slots ``slots[b]``."""
+
+    def __init__(self, lengths, starts=None, slots=None):
+        starts = starts or [0] * len(lengths)
+        self.num_requests = len(lengths)
+        cu = np.concatenate([[0], np.cumsum(lengths)])
+        self.cu_q = torch.tensor(cu, dtype=torch.int32, device=DEV)
+        self.positions = torch.tensor(np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lengths)]),
+                                      dtype=torch.int32, device=DEV)
+        self.state_slots = torch.tensor(slots or list(range(len(lengths))), dtype=torch.int32, device=DEV)
+        self.fresh = torch.tensor([int(s == 0) for s in starts], dtype=torch.int32, device=DEV)
+
+
+class Tables:
+    def __init__(self, dims, base, n):
+        from tinyserve_b200.parts.rotary import Rotary
+        self.rotary_dim, self.interleaved = dims, False
+        cos, sin = Rotary.tables(dims, base, n)
+        self.cos, self.sin = cos.to(DEV), sin.to(DEV)
+
+
+def draws(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).bfloat16().double()
+
+
+def on_device(x, dtype):
+    return x.to(dtype).to(DEV).contiguous()
+
+
+# ----------------------------------------------------------------------------- mechanisms alone
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
+def test_layer_norm_adds_both_addends_in_32_bit(dtype, tol):
+    from tinyserve_b200.kernels import ops
+    T, n = 37, 200
+    r, a, b, w = draws(T, n, seed=1, scale=3.0), draws(T, n, seed=2), draws(T, n, seed=3), draws(n, seed=4) + 1.0
+    r = r + 5.0                                   # a mean far from zero: the variance is of the deviations
+    residual = on_device(r, torch.float32)
+    out = ops.add_layernorm(ops.PairSum(on_device(a, dtype), on_device(b, dtype)), residual, on_device(w, dtype), 1e-5, dtype)
+    want = plain.layer_norm(r + a + b, w, 1e-5)
+    assert (out.double().cpu() - want).abs().max() <= tol * want.abs().max()
+    assert (residual.double().cpu() - (r + a + b)).abs().max() <= 1e-6 * (r.abs().max() + 2)
+    rows = torch.tensor([5, 0, 36], dtype=torch.int32, device=DEV)
+    before = residual.clone()
+    some = ops.add_layernorm(on_device(a, dtype), residual, on_device(w, dtype), 1e-5, dtype, rows=rows)
+    assert torch.equal(before, residual), "with rows the residual is left as it is"
+    want = plain.layer_norm((before.double().cpu() + a)[[5, 0, 36]], w, 1e-5)
+    assert (some.double().cpu() - want).abs().max() <= tol * want.abs().max()
+
+
+def test_soft_cap_and_row_vector():
+    from tinyserve_b200.kernels import ops
+    y = draws(9, 301, seed=5, scale=20.0)
+    got = ops.softcap_(on_device(y, torch.float32), 7.5)
+    assert (got.double().cpu() - plain.soft_cap(y, 7.5)).abs().max() < 2e-6 * 7.5
+    x, v = draws(6, 40, seed=6), draws(40, seed=7)
+    got = ops.add_row_vector_(on_device(x, torch.float32), on_device(v, torch.bfloat16))
+    assert (got.double().cpu() - (x + v)).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 8e-3)])
+def test_mean_of_normed_branches_and_stream_concat(dtype, tol):
+    from tinyserve_b200.kernels import ops
+    T, n, eps = 19, 72, 1e-4
+    a, b = draws(T, n, seed=8, scale=4.0), draws(T, n, seed=9, scale=0.1)
+    wa, wb = draws(n, seed=10) + 1, draws(n, seed=11) + 1
+    got = ops.mean_of_normed([on_device(a, dtype), on_device(b, dtype)], [on_device(wa, dtype), on_device(wb, dtype)], eps)
+    want = 0.5 * (plain.unit_rms(a, eps) * wa + plain.unit_rms(b, eps) * wb)
+    assert (got.double().cpu() - want).abs().max() <= tol * want.abs().max()
+    r, first = draws(T, n, seed=12), draws(T, n, seed=13)
+    both = ops.stream_concat(on_device(r, torch.float32), ops.PairSum(on_device(a, dtype), on_device(b, dtype)),
+                             on_device(first, torch.float32), dtype)
+    want = torch.cat([r + a + b, first], -1)
+    assert (both.double().cpu() - want).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-6), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("H,G,n,nv,rot", [(4, 2, 16, 32, 16), (3, 3, 48, 16, 24), (2, 1, 32, 32, 0)])
+def test_rotation_unit_norm_and_padded_cache_write(dtype, tol, H, G, n, nv, rot):
+    """q and k turned, divided by their root mean square, stored D wide with zeros behind; a
+    request that stands at position 40 and one that starts."""
+    from tinyserve_b200.kernels import ops
+    lengths, starts = [5, 3], [40, 0]
+    T, D, page, eps = 8, -(-max(n, nv) // 16) * 16, 4, 1e-3
+    q, k, v = draws(T, H * n, seed=14), draws(T, G * n, seed=15), draws(T, G * nv, seed=16)
+    batch = Batch(lengths, starts)
+    fused = on_device(torch.cat([q, k, v], -1), dtype)
+    k_cache = torch.full((12, G, page, D), 7.0, dtype=dtype, device=DEV)
+    v_cache = torch.full((12, G, page, D), 7.0, dtype=dtype, device=DEV)
+    slots = torch.tensor([9, 10, 11, 4, 5, 20, 21, 22], dtype=torch.int32, device=DEV)
+    got = ops.rope_unit_kvwrite(fused[:, :H * n], fused[:, H * n:H * n + G * n], fused[:, H * n + G * n:], batch.positions,
+                                H, G, n, nv, D, rotary=Tables(rot, 1e4, 64) if rot else None, unit_norm=True, eps=eps,
+                                k_cache=k_cache, v_cache=v_cache, slot_mapping=slots, page_size=page)
+    pos = batch.positions.cpu().long()
+    want_q = plain.unit_rms(plain.rotate(q.view(T, H, n), pos, rot, 1e4), eps)
+    want_k = plain.unit_rms(plain.rotate(k.view(T, G, n), pos, rot, 1e4), eps)
+    assert (got[..., :n].double().cpu() - want_q).abs().max() <= tol * want_q.abs().max()
+    assert not got[..., n:].any()
+    flat_k, flat_v = k_cache.transpose(1, 2).reshape(-1, G, D), v_cache.transpose(1, 2).reshape(-1, G, D)
+    assert (flat_k[slots.long()][..., :n].double().cpu() - want_k).abs().max() <= tol * want_k.abs().max()
+    assert not flat_k[slots.long()][..., n:].any() and not flat_v[slots.long()][..., nv:].any()
+    assert (flat_v[slots.long()][..., :nv].double().cpu() - v.view(T, G, nv)).abs().max() <= tol * v.abs().max()
+    untouched = torch.ones(48, dtype=torch.bool)
+    untouched[slots.long().cpu()] = False
+    assert (flat_k[untouched.to(DEV)] == 7.0).all(), "only the tokens' own slots are written"
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("kind", ["per_head", "per_channel"])
+@pytest.mark.parametrize("H,n,nv", [(2, 16, 32), (3, 20, 24), (1, 64, 128)])
+def test_matrix_state_scan_in_portions_from_and_to_slots(dtype, tol, kind, H, n, nv):
+    """Three requests of unequal length, cut into steps of unequal portions (one token, two,
+    seventeen: across the staging of sixteen), with state slots in another order than the
+    requests; a slot that held another request's state before.  Against one scan over each whole
+    sequence."""
+    from tinyserve_b200.kernels import ops
+    lengths, eps, tau = [41, 1, 23], 1e-5, 3.0
+    T = sum(lengths)
+    q, k, v, g = (draws(T, H * n, seed=20), draws(T, H * n, seed=21), draws(T, H * nv, seed=22), draws(T, H * nv, seed=23))
+    z = draws(T, H * n, seed=24, scale=2.0) + 3.0            # decays near one: a long memory
+    decay = [0.999, 0.9, 0.99][:H]
+    w = draws(nv, seed=25) + 1
+    rot = Tables(n // 2 // 2 * 2, 100.0, 64) if kind == "per_head" else None
+    bounds = np.concatenate([[0], np.cumsum(lengths)])
+    want = torch.zeros(T, H * nv, dtype=torch.float64)
+    for b, n_tok in enumerate(lengths):
+        s = slice(bounds[b], bounds[b + 1])
+        pos = torch.arange(n_tok)
+        qq, kk = q[s].view(n_tok, H, n), k[s].view(n_tok, H, n)
+        if kind == "per_head":
+            qq, kk = plain.rotate(qq, pos, rot.rotary_dim, 100.0), plain.rotate(kk, pos, rot.rotary_dim, 100.0) * n ** -0.5
+        else:
+            qq = qq * n ** -0.5
+        for a in range(H):
+            d = torch.full((n_tok, n), decay[a], dtype=torch.float64) if kind == "per_head" else \
+                torch.sigmoid(z[s].view(n_tok, H, n)[:, a]).pow(1 / tau)
+            o = plain.unit_rms(plain.matrix_state_scan(qq[:, a], kk[:, a], v[s].view(n_tok, H, nv)[:, a], d), eps)
+            if kind == "per_channel":
+                o = o * w
+            want[s, a * nv:(a + 1) * nv] = o * plain.silu(g[s, a * nv:(a + 1) * nv])
+    state = torch.full((5, H, n, nv), 3.0, dtype=torch.float32, device=DEV)      # what another request left
+    slot_of = [4, 0, 2]
+    done = [0, 0, 0]
+    got = torch.zeros(T, H * nv, dtype=torch.float64)
+    for portions in ([17, 1, 2], [1, 0, 17], [2, 0, 4], [21, 0, 0]):
+        live = [b for b in range(3) if portions[b]]
+        rows = np.concatenate([np.arange(bounds[b] + done[b], bounds[b] + done[b] + portions[b]) for b in live])
+        batch = Batch([portions[b] for b in live], [done[b] for b in live], [slot_of[b] for b in live])
+        fused = on_device(torch.cat([q, k, v, g], -1)[rows], dtype)
+        qs, ks, vs = fused[:, :H * n], fused[:, H * n:2 * H * n], fused[:, 2 * H * n:2 * H * n + H * nv]
+        kw = dict(decay=torch.tensor(decay, dtype=torch.float32, device=DEV), rotary=rot, k_scale=n ** -0.5) \
+            if kind == "per_head" else dict(decay_logits=on_device(z[rows], torch.float32), tau=tau, q_scale=n ** -0.5,
+                                            norm_weight=on_device(w, dtype))
+        out = ops.linear_attention(qs, ks, vs, fused[:, 2 * H * n + H * nv:], state, batch, H, n, nv, dtype, eps=eps, **kw)
+        got[rows] = out.double().cpu()
+        for b in live:
+            done[b] += portions[b]
+    assert done == lengths
+    assert (got - want).abs().max() <= tol * want.abs().max()
+    assert (state[[1, 3]] == 3.0).all(), "slots of no request are left alone"
+
+
+# ----------------------------------------------------------------------------- whole models
+LENGTHS = {"X": [5, 17, 40, 70, 2, 1, 33], "Y": [1, 9, 64, 100, 31, 48], "Z": [150, 260, 57, 3, 129]}
+
+
+@pytest.fixture(scope="module", params=sorted(DUDATAR_TINY))
+def model(request, tmp_path_factory):
+    name = request.param
+    folder = make_dudatar_dir(tmp_path_factory.mktemp(f"dudatar{name}"), name, seed=41)
+    cfg, weights = plain.load_folder(folder)
+    reqs = {f"r{i}": random_ids(cfg["vocab"], n, seed=300 + i) for i, n in enumerate(LENGTHS[name])}
+    ref = {rid: plain.logits(cfg, weights, ids) for rid, ids in reqs.items()}
+    return {"name": name, "folder": folder, "cfg": cfg, "weights": weights, "requests": reqs, "ref": ref}
+
+
+def run_replay(folder, dtype, steps, out_dir, page=16, max_live=4, graphs=False):
+    from tinyserve_b200.engine import replay
+    runner = replay.make_runner(folder, dtype, max_live_tokens(steps, max(64, page)), block_size=page,
+                                max_live=max_live, use_cuda_graphs=graphs)
+    done = []
+    replay.replay(runner, lines_of(steps), str(out_dir), done.append)
+    assert done == [f"done {s['step']}" for s in steps]
+    runner.manager.check_invariants()
+    assert not runner.manager.requests and all(p.num_free == p.num_usable for p in runner.manager.pools)
+    outputs = {}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        if wanted:
+            data = np.fromfile(os.path.join(str(out_dir), f"{s['step']}.f32"), dtype="<f4")
+            outputs[s["step"]] = torch.from_numpy(data.reshape(wanted, runner.model.vocab_size))
+    return outputs, runner
+
+
+def check(model, dtype, steps, out_dir, slack=1.0, **kw):
+    outputs, runner = run_replay(model["folder"], dtype, steps, out_dir, **kw)
+    got = collect_logits(steps, outputs, model["cfg"]["vocab"])
+    for rid, out in got.items():
+        ref = model["ref"][rid.rstrip("x")]
+        assert out.shape == ref.shape
+        scale = ref.abs().max().item()
+        err = (out.double() - ref).abs().max(-1).values / scale
+        rms = (out.double() - ref).pow(2).mean(-1).sqrt() / scale
+        seen = MEASURED.setdefault((model["name"], dtype), [0.0, 0.0])
+        seen[0], seen[1] = max(seen[0], err.max().item()), max(seen[1], rms.max().item())
+        tol, tol_rms = TOLERANCE[dtype], RMS_TOLERANCE[dtype]
+        if dtype == "bfloat16":
+            tol, tol_rms = tol[model["name"][0]], tol_rms[model["name"][0]]
+        bad = ((err > slack * tol) | (rms > slack * tol_rms)).nonzero()
+        assert bad.numel() == 0, (f"{model['name']} {dtype} request {rid}: first wrong token at place {int(bad[0])} "
+                                  f"(error {err[int(bad[0])]:.3e}, rms {rms[int(bad[0])]:.3e})")
+    return runner
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_prompts(model, dtype, tmp_path):
+    check(model, dtype, schedule_whole(model["requests"]), tmp_path)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_against_token_by_token(model, dtype, tmp_path):
+    """The last 32 tokens one by one; and everything but the first token one by one (the first
+    tokens of a sequence, and a long run of decoding)."""
+    check(model, dtype, schedule_tail_decode(model["requests"], 32), tmp_path / "tail")
+    longest = max(model["requests"], key=lambda r: len(model["requests"][r]))
+    one = {longest: model["requests"][longest]}
+    check(model, dtype, schedule_tail_decode(one, len(one[longest]) - 1), tmp_path / "all", graphs=dtype == "bfloat16")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_down_to_two_tokens(model, dtype, tmp_path):
+    check(model, dtype, schedule_portions(model["requests"]), tmp_path / "a")
+    check(model, dtype, schedule_portions(model["requests"], sizes=(2,)), tmp_path / "twos")
+    check(model, dtype, schedule_portions(model["requests"], sizes=(16, 1, 15, 17, 32, 3)), tmp_path / "edges", page=8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [0, 1])
+def test_mixed_batches_reuse_pages_and_slots(model, dtype, seed, tmp_path):
+    reqs = dict(model["requests"])
+    more = {f"{rid}x": ids for rid, ids in reqs.items()}
+    steps = schedule_mixed({**reqs, **more}, max_live=4, seed=seed)
+    assert max(len(s["entries"]) for s in steps) >= 3
+    assert any(len({len(e["tokens"]) == 1 for e in s["entries"]}) == 2 for s in steps), "portions beside single tokens"
+    runner = check(model, dtype, steps, tmp_path, max_live=4)
+    assert len(reqs) + len(more) > runner.manager.slots.num_slots == 4, "state slots are used again"
+    if runner.manager.pools:
+        total = sum(-(-len(i) // 16) for i in {**reqs, **more}.values())
+        assert total > runner.manager.pools[0].num_usable, "the pool is too small to avoid reuse"
+
+
+def test_batch_of_unequal_requests_equals_each_alone(model, tmp_path):
+    """One step with all prompts against one step each: the same bits in 32-bit (every product
+    sums in the same order whatever else is in the batch)."""
+    reqs = model["requests"]
+    together = [{"step": 0, "entries": [{"id": r, "tokens": ids, "want": list(range(len(ids)))} for r, ids in reqs.items()],
+                 "end": list(reqs)}]
+    out_a, _ = run_replay(model["folder"], "float32", together, tmp_path / "a", max_live=len(reqs))
+    out_b, _ = run_replay(model["folder"], "float32", schedule_whole(reqs), tmp_path / "b")
+    a = collect_logits(together, out_a, model["cfg"]["vocab"])
+    b = collect_logits(schedule_whole(reqs), out_b, model["cfg"]["vocab"])
+    for rid in reqs:
+        # (the attention kernel cuts a request's keys into ranges by how full the batch is: the
+        # order of its sums, not what is summed, depends on the batch)
+        assert (a[rid] - b[rid]).abs().max() <= 1e-5 * b[rid].abs().max()
+
+
+# ----------------------------------------------------------------------------- weights that show a fault
+def sharpened(folder, out, cfg):
+    """The same model with its memories made long and its attention sharp: the decay logits of
+    the gated layers shifted up (decays near one), the retention decays near one, a large
+    attention scale: a far key, a lost state or a wrong position then moves the logits."""
+    weights = load_file(os.path.join(folder, "model.safetensors"))
+    cfg = {**cfg, "layers": [dict(layer) for layer in cfg["layers"]]}
+    for i, layer in enumerate(cfg["layers"]):
+        if layer["type"] == "gla":
+            weights[f"l{i}.mix.a2.b"] = (weights[f"l{i}.mix.a2.b"].float() + 6.0).bfloat16()
+        else:
+            m = {**layer["mixer"], "left": dict(layer["mixer"]["left"]), "right": dict(layer["mixer"]["right"])}
+            m["left"]["scale"] = 1.5
+            m["right"]["decay"] = [1.0 - 2.0 ** -(6 + a) for a in range(m["right"]["heads"])]
+            layer["mixer"] = m
+    os.makedirs(out, exist_ok=True)
+    save_file(weights, os.path.join(out, "model.safetensors"))
+    import json
+    with open(os.path.join(out, "config.json"), "w") as fh:
+        json.dump(cfg, fh)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_keys_and_long_memories(dtype, tmp_path):
+    folder = make_dudatar_dir(tmp_path / "base", "Z", seed=43)
+    cfg, _ = plain.load_folder(folder)
+    sharp = sharpened(folder, str(tmp_path / "sharp"), cfg)
+    cfg, weights = plain.load_folder(sharp)
+    ids = random_ids(cfg["vocab"], 200, seed=7)
+    # the token at place 3 comes back at places 130 and 199: with unit-norm keys and a large scale the
+    # queries there find it again across eight pages
+    ids[130] = ids[199] = ids[3]
+    reqs = {"far": ids, "near": ids[:70]}
+    ref = {rid: plain.logits(cfg, weights, t) for rid, t in reqs.items()}
+    short = plain.logits(cfg, weights, ids[60:])                 # the same tail without what lies far back
+    assert (short[-1] - ref["far"][-1]).abs().max() > 0.05 * ref["far"].abs().max(), "the far tokens matter here"
+    model = {"name": "Zsharp", "folder": sharp, "cfg": cfg, "requests": reqs, "ref": ref}
+    # (sums over hundreds of tokens that hardly decay, and a softmax that leans on single keys:
+    # twice the rounding of the models above; measured 8.8e-5 and 2.6e-5 in float32)
+    check(model, dtype, schedule_whole(reqs), tmp_path / "whole", slack=2.0)
+    check(model, dtype, schedule_tail_decode(reqs, 40), tmp_path / "tail", slack=2.0)
+    check(model, dtype, schedule_portions(reqs, sizes=(63, 2, 1, 64, 5, 16, 15)), tmp_path / "portions", slack=2.0)
+    check(model, dtype, schedule_mixed({**reqs, "farx": ids, "nearx": ids[:70]}, max_live=3, seed=5), tmp_path / "mixed",
+          slack=2.0, max_live=3)
+
+
+# ----------------------------------------------------------------------------- the entry point
+def test_greedy_generation_through_the_scheduler(tmp_path):
+    """Five prompts of unequal length through LLM.generate with three state slots and a budget of
+    48 tokens a step (prompts in portions beside decoding requests, slots and pages used again)."""
+    from tinyserve_b200 import LLM, SamplingParams
+    folder = make_dudatar_dir(tmp_path, "X", seed=44)
+    cfg, weights = plain.load_folder(folder)
+    prompts = [random_ids(cfg["vocab"], n, seed=500 + n) for n in (3, 60, 17, 1, 90)]
+    params = SamplingParams(temperature=0.0, max_tokens=12, repetition_penalty=1.0, ignore_eos=True)
+    llm = LLM(folder, dtype="float32", max_model_len=128, block_size=16, max_num_seqs=3, max_num_batched_tokens=48,
+              num_blocks=20, use_cuda_graphs=False)
+    outs = llm.generate(prompts, params)
+    for prompt, out in zip(prompts, outs):
+        want, gaps = plain.greedy(cfg, weights, prompt, 12)
+        assert out.finished and len(out.token_ids) == 12
+        for j, (a, b, gap) in enumerate(zip(out.token_ids, want, gaps)):
+            if gap < 1e-3:
+                break                        # a near tie: either side is a right answer, the rest differs
+            assert a == b, (len(prompt), j)
+    outs16 = LLM(folder, dtype="bfloat16", max_model_len=128, block_size=16, max_num_seqs=3,
+                 max_num_batched_tokens=48, num_blocks=20, use_cuda_graphs=True).generate(prompts, params)
+    for prompt, out in zip(prompts, outs16):
+        ids = list(prompt)
+        for tok in out.token_ids:
+            row = plain.logits(cfg, weights, ids)[-1]
+            assert row[tok] >= row.max() - 0.05 * row.abs().max()
+            ids.append(tok)
+
+
+def test_measured_differences_are_reported():
+    print({k: (f"{v[0]:.2e}", f"{v[1]:.2e}") for k, v in sorted(MEASURED.items())})
