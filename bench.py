@@ -13,6 +13,12 @@ A step is one decode step of the whole batch.  Prints ONE JSON line:
   roofline  bytes the decode step must read (every weight once + the live cache) / time
   points    decode tokens per second at batch 1 and 64
 The engine runs on one GPU; with --gpus > 1 it says so and exits with 2.
+
+    python bench.py --arch dudatar [--sizes 2048,4096]
+
+measures another design beside Qwen3 at equal size instead (random weights, same width, block
+runs, feed-forward width, heads and vocabulary): prefill of one 2,048-token prompt, decode at
+batch 8, and the design's own kernels beside the like kernels of Qwen3, each against its roofline.
 """
 from __future__ import annotations
 
@@ -328,6 +334,137 @@ def run_long_context(seed, steps, warmup, block_size=16):
     return out
 
 
+# ----------------------------------------------------------------------------- another design beside Qwen3
+def dudatar_shapes(width):
+    """A Dudatar of real layer sizes at ``width``: a gated layer, two layers of attention beside
+    retention (this pair runs twice), a gated layer: six block runs; and the Qwen3 of the same
+    width, block runs, feed-forward width, attention heads and vocabulary."""
+    heads, ff, vocab = width // 128, width * 11 // 4, 32768
+    rot = lambda dims: {"dims": dims, "base": 1e6}
+    gla = {"type": "gla", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0, "rank": 16}}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+        "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot(64)},
+        "right": {"heads": heads // 2, "dim": 128, "vdim": 256, "rot": rot(128),
+                  "decay": [1.0 - 2.0 ** -(5 + 5 * i / max(1, heads // 2 - 1)) for i in range(heads // 2)]}}}
+    dudatar = {"architecture": "Dudatar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+               "loop": {"start": 1, "stop": 3, "times": 2}, "layers": [gla, par, par, gla]}
+    qwen3 = dict(QWEN3_8B, hidden_size=width, num_hidden_layers=6, num_attention_heads=heads,
+                 num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=ff, vocab_size=vocab)
+    return dudatar, qwen3
+
+
+def _time_us(fn, iters=20):
+    import torch
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) * 1e3 / iters
+
+
+def kernel_table(width, peaks):
+    """The design's own kernels beside the like kernels of Qwen3 at this width, one launch each
+    (operands larger than L2 where the size allows: 2,048 tokens of prefill; at decode the state
+    and the cache of 8 requests), time over roofline time.  Roofline of the matrix-state scan: the
+    slower of its bytes over the copy bandwidth and its 32-bit multiply-adds over the FMA rate of
+    the CUDA cores (SMs x 128 lanes x 2 x the maximum clock): its arithmetic is 32-bit by design."""
+    import torch
+    from types import SimpleNamespace
+    from tinyserve_b200.kernels import ops
+    dev, bf = "cuda:0", torch.bfloat16
+    heads = width // 128
+    H, n, nv = heads // 2, 128, 256
+    fma_tflops = ops.num_sms() * 128 * 2 * 1.965e9 / 1e12
+    out = {}
+    for name, lengths, starts in (("prefill_2048", [2048], [0]), ("decode_b8", [1] * 8, [512] * 8)):
+        T, B = sum(lengths), len(lengths)
+        cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=dev)
+        ctx = SimpleNamespace(num_requests=B, cu_q=cu, state_slots=torch.arange(B, dtype=torch.int32, device=dev),
+                              fresh=torch.zeros(B, dtype=torch.int32, device=dev),
+                              positions=torch.cat([torch.arange(s, s + m) for s, m in zip(starts, lengths)]).int().to(dev))
+        proj = torch.randn(T, 2 * H * n + 2 * H * nv, device=dev).to(bf)
+        q, k, v, g = proj[:, :H * n], proj[:, H * n:2 * H * n], proj[:, 2 * H * n:2 * H * n + H * nv], proj[:, 2 * H * n + H * nv:]
+        z = torch.randn(T, H * n, device=dev) + 3
+        state = torch.zeros(B, H, n, nv, device=dev)
+        decay = torch.full((H,), 0.99, device=dev)
+        w = torch.ones(nv, device=dev, dtype=bf)
+        flops = 4.0 * T * H * n * nv
+        nbytes = T * (2 * H * n + 3 * H * nv) * 2 + 2 * B * H * n * nv * 4
+        for kind, kw in (("retention", dict(decay=decay, k_scale=n ** -0.5)),
+                         ("gla", dict(decay_logits=z, tau=16.0, q_scale=n ** -0.5, norm_weight=w))):
+            us = _time_us(lambda: ops.linear_attention(q, k, v, g, state, ctx, H, n, nv, bf, eps=1e-5, **kw))
+            extra = T * H * n * 4 if kind == "gla" else 0
+            roof = max((nbytes + extra) / (peaks["hbm_gbs"] * 1e3), flops / (fma_tflops * 1e6))
+            out[f"{kind}_scan_{name}"] = {"us": round(us, 1), "roofline_us": round(roof, 1), "frac": round(roof / us, 3)}
+        # the attention kernel both designs run, at the left mixer's (= Qwen3's) sizes
+        Ha, G, D, page = heads, max(1, heads // 4), 128, 64
+        kv_len = starts[0] + lengths[0]
+        pages_per = -(-kv_len // page)
+        kc = torch.randn(B * pages_per + 1, G, page, D, device=dev).to(bf)
+        vc = torch.randn_like(kc)
+        table = (torch.arange(B * pages_per, dtype=torch.int32, device=dev) + 1).view(B, pages_per)
+        from tinyserve_b200.engine.batch import GroupView, StepContext
+        sc = StepContext()
+        sc.num_tokens, sc.num_requests, sc.max_q_len, sc.max_kv_len = T, B, max(lengths), kv_len
+        sc.cu_q, sc.kv_lens = cu, torch.full((B,), kv_len, dtype=torch.int32, device=dev)
+        sc.host = {"cu_q": cu.tolist(), "kv_lens": [kv_len] * B}
+        view = GroupView(page, pages_per, None, table, kc.shape[0])
+        qa = torch.randn(T, Ha, D, device=dev).to(bf)
+        us = _time_us(lambda: ops.paged_attention(qa, kc, vc, view, sc, D ** -0.5))
+        if T > B:
+            roof = 4.0 * Ha * D * T * (T + 1) / 2 / (peaks["bf16_tflops"] * 1e6)
+        else:
+            roof = B * kv_len * 2 * G * D * 2 / (peaks["hbm_gbs"] * 1e3)
+        out[f"attention_{name}"] = {"us": round(us, 1), "roofline_us": round(roof, 1), "frac": round(roof / us, 3)}
+        # the norms: layer norm with two addends beside residual add + RMSNorm
+        res = torch.randn(T, width, device=dev)
+        a1, a2 = torch.randn(T, width, device=dev).to(bf), torch.randn(T, width, device=dev).to(bf)
+        wn = torch.ones(width, device=dev, dtype=bf)
+        us_ln = _time_us(lambda: ops.add_layernorm(ops.PairSum(a1, a2), res, wn, 1e-5, bf))
+        us_rms = _time_us(lambda: ops.add_rmsnorm(a1, res, wn, 1e-5, bf))
+        for key, us, addends in (("add_layernorm", us_ln, 2), ("add_rmsnorm", us_rms, 1)):
+            roof = T * width * (8 + 2 * addends + 2) / (peaks["hbm_gbs"] * 1e3)
+            out[f"{key}_{name}"] = {"us": round(us, 1), "roofline_us": round(roof, 2), "frac": round(roof / us, 3)}
+    return out
+
+
+def arch_main(a) -> int:
+    """``--arch dudatar``: the design beside Qwen3 at equal size.  One JSON line."""
+    import torch
+    from tinyserve_b200 import LLM
+    from tinyserve_b200.config import config_from_dict
+    peaks = load_peaks()
+    warmup, steps = max(a.warmup, 3), min(a.steps, 64)
+    sizes = {}
+    for width in [int(w) for w in a.sizes.split(",")]:
+        entry = {}
+        for name, raw in zip(("dudatar", "qwen3"), dudatar_shapes(width)):
+            llm = LLM(model_config=config_from_dict(raw), random_weights=True, dtype="bfloat16", max_model_len=CONTEXT,
+                      block_size=a.block_size, max_num_seqs=8, max_num_batched_tokens=PREFILL_TOKENS,
+                      num_blocks=8 * (CONTEXT // a.block_size) // 2 + 4096 // a.block_size, use_cuda_graphs=False, seed=a.seed)
+            llm.runner.capture_decode_graphs([8])
+            dec = run_decode(llm, 8, steps, warmup, a.seed)
+            ms = run_prefill(llm, a.seed)
+            entry[name] = {"decode_b8_tok_s": round(dec["tok_s"], 1), "decode_ms": round(dec["ms"], 4),
+                           "decode_launches_per_step": dec["launches"] // steps,
+                           "prefill_2048_tok_s": round(PREFILL_TOKENS * 1000.0 / ms, 1), "prefill_ms": round(ms, 3),
+                           "weight_gib": round(llm.runner.weight_bytes / 2 ** 30, 3)}
+            _release(llm)
+            llm = None
+        entry["kernels"] = kernel_table(width, peaks)
+        sizes[str(width)] = entry
+    print(json.dumps({"metric": "prefill and decode tok/s, Dudatar beside Qwen3 at equal size (random weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "steps": steps,
+                      "warmup": warmup, "block_runs": 6, "sizes": sizes, "peaks": peaks}))
+    return 0
+
+
 def reference_main(a) -> int:
     """``--impl reference``: priyammaz/tinyserve, unmodified, from baseline/_ref, through its own
     Engine (see baseline/reference_arm.py).  If it cannot start here, the line says why."""
@@ -366,9 +503,17 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the 0.6B burst, the 32B run and the long-context decode")
+    ap.add_argument("--arch", choices=["qwen3", "dudatar"], default="qwen3",
+                    help="dudatar: measure that design beside Qwen3 at equal size instead of the default workload")
+    ap.add_argument("--sizes", default="2048,4096", help="--arch dudatar: model widths to measure")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_main(a)
+    if a.arch == "dudatar":
+        if a.gpus != 1:
+            print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+            return 2
+        return arch_main(a)
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2

@@ -142,12 +142,14 @@ def test_rotation_unit_norm_and_padded_cache_write(dtype, tol, H, G, n, nv, rot)
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
 @pytest.mark.parametrize("kind", ["per_head", "per_channel"])
-@pytest.mark.parametrize("H,n,nv", [(2, 16, 32), (3, 20, 24), (1, 64, 128)])
-def test_matrix_state_scan_in_portions_from_and_to_slots(dtype, tol, kind, H, n, nv):
+@pytest.mark.parametrize("H,n,nv", [(2, 16, 32), (3, 20, 24), (1, 64, 128), (2, 16, 160)])
+@pytest.mark.parametrize("segment", [0, 16])
+def test_matrix_state_scan_in_portions_from_and_to_slots(dtype, tol, kind, H, n, nv, segment):
     """Three requests of unequal length, cut into steps of unequal portions (one token, two,
     seventeen: across the staging of sixteen), with state slots in another order than the
     requests; a slot that held another request's state before.  Against one scan over each whole
-    sequence."""
+    sequence.  With ``segment`` the portions are cut into segments of sixteen tokens that run side
+    by side (a portion of 17 or 21 tokens is two segments, the second one short)."""
     from tinyserve_b200.kernels import ops
     lengths, eps, tau = [41, 1, 23], 1e-5, 3.0
     T = sum(lengths)
@@ -186,7 +188,7 @@ def test_matrix_state_scan_in_portions_from_and_to_slots(dtype, tol, kind, H, n,
         kw = dict(decay=torch.tensor(decay, dtype=torch.float32, device=DEV), rotary=rot, k_scale=n ** -0.5) \
             if kind == "per_head" else dict(decay_logits=on_device(z[rows], torch.float32), tau=tau, q_scale=n ** -0.5,
                                             norm_weight=on_device(w, dtype))
-        out = ops.linear_attention(qs, ks, vs, fused[:, 2 * H * n + H * nv:], state, batch, H, n, nv, dtype, eps=eps, **kw)
+        out = ops.linear_attention(qs, ks, vs, fused[:, 2 * H * n + H * nv:], state, batch, H, n, nv, dtype, eps=eps, segment=segment, **kw)
         got[rows] = out.double().cpu()
         for b in live:
             done[b] += portions[b]

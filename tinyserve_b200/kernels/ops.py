@@ -1223,7 +1223,15 @@ def head_gate(attn, gate, vdim):
 
 
 # ----------------------------------------------------------------------------- linear attention with a matrix state
-LINEAR_ATTENTION_MAX_VALUE_DIM = 256
+LINEAR_ATTENTION_MAX_VALUE_DIM = 4096
+#: value columns of a head that one block of the scan takes; wider heads are spread over several
+#: blocks and their output norm runs as a kernel of its own
+LINEAR_ATTENTION_BLOCK_COLUMNS = 128
+#: a step whose longest portion has at least LINEAR_ATTENTION_SEGMENT_MIN tokens cuts its portions
+#: into segments of LINEAR_ATTENTION_SEGMENT tokens that run side by side (three launches instead
+#: of one: local states, their combination, outputs)
+LINEAR_ATTENTION_SEGMENT = 128
+LINEAR_ATTENTION_SEGMENT_MIN = 256
 
 
 def _linear_attention(key_dim: int):
@@ -1233,14 +1241,16 @@ def _linear_attention(key_dim: int):
 
 
 def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, out_dtype, *, decay=None,
-                     decay_logits=None, tau=1.0, rotary=None, q_scale=1.0, k_scale=1.0, norm_weight=None, eps=0.0):
+                     decay_logits=None, tau=1.0, rotary=None, q_scale=1.0, k_scale=1.0, norm_weight=None, eps=0.0,
+                     segment=None):
     """Per request and head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over this step's
     tokens, from and to ``state`` [slots, H, key_dim, value_dim] (float32) at the requests' state
     slots (``ctx.state_slots``, ``ctx.fresh``, ``ctx.cu_q``); returns [T, H * value_dim] =
     o / rms(o) (* norm_weight) * silu(gate).  a_t: ``decay`` float32 [H] (one constant per head)
     or ``decay_logits`` float32 [T, H * key_dim] with a = sigmoid(z)^(1 / tau).  q, k [T, H key_dim],
     v, gate [T, H value_dim] may be column ranges of one projection.  ``rotary``: positions on q
-    and k; ``q_scale`` / ``k_scale``: constant factors (after the rotation)."""
+    and k; ``q_scale`` / ``k_scale``: constant factors (after the rotation).  ``segment``: tokens per
+    segment of the side-by-side form (None: chosen by the step's longest portion, 0: never)."""
     _cuda(q, k, v, gate, state, decay, decay_logits, norm_weight)
     T = q.shape[0]
     H = num_heads
@@ -1255,6 +1265,18 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
     out = torch.empty(T, H * value_dim, dtype=out_dtype, device=q.device)
     zp, zld = _columns(decay_logits) if decay_logits is not None else (c_void_p(0), c_longlong(0))
     gp, gld = _columns(gate) if gate is not None else (c_void_p(0), c_longlong(0))
+    if segment is None:
+        seg_len = LINEAR_ATTENTION_SEGMENT if getattr(ctx, "max_q_len", 0) >= LINEAR_ATTENTION_SEGMENT_MIN else 0
+    else:
+        seg_len = int(segment)
+    max_segments, seg_state, seg_decay = 0, None, None
+    if seg_len:
+        max_segments = -(-(getattr(ctx, "max_q_len", 0) or T) // seg_len)
+        seg_state = torch.empty(ctx.num_requests * H * max_segments * key_dim * value_dim, dtype=torch.float32, device=q.device)
+        if decay_logits is not None:
+            seg_decay = torch.empty(ctx.num_requests * H * max_segments * key_dim, dtype=torch.float32, device=q.device)
+    wide = value_dim > LINEAR_ATTENTION_BLOCK_COLUMNS
+    raw = torch.empty(T, H * value_dim, dtype=torch.float32, device=q.device) if wide else None
     lib = _linear_attention(key_dim)
     _check(lib, lib.ts_linear_attention(
         c_int(_dt(q)), *_columns(q), *_columns(k), *_columns(v), gp, gld, zp, zld, c_float(tau), _ptr(decay),
@@ -1262,5 +1284,6 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
         _ptr(rotary.sin if rotary is not None else None), c_int(rotary.rotary_dim if rotary is not None else 0),
         c_float(q_scale), c_float(k_scale), _ptr(state), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(ctx.cu_q),
         c_int(ctx.num_requests), _ptr(norm_weight), c_int(_vec_flag(norm_weight, out_dtype) if norm_weight is not None else 0),
-        c_float(eps), _ptr(out), c_longlong(out.stride(0)), c_int(H), c_int(value_dim), _stream()))
+        c_float(eps), _ptr(out), c_longlong(out.stride(0)), c_int(H), c_int(value_dim), c_int(seg_len), _ptr(seg_state),
+        _ptr(seg_decay), c_int(max_segments), c_int(T), _ptr(raw), _stream()), (3 if seg_len else 1) + int(wide))
     return out
