@@ -385,7 +385,8 @@ def kernel_table(width, peaks):
     for name, lengths, starts in (("prefill_2048", [2048], [0]), ("decode_b8", [1] * 8, [512] * 8)):
         T, B = sum(lengths), len(lengths)
         cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=dev)
-        ctx = SimpleNamespace(num_requests=B, cu_q=cu, state_slots=torch.arange(B, dtype=torch.int32, device=dev),
+        ctx = SimpleNamespace(num_requests=B, cu_q=cu, max_q_len=max(lengths),
+                              state_slots=torch.arange(B, dtype=torch.int32, device=dev),
                               fresh=torch.zeros(B, dtype=torch.int32, device=dev),
                               positions=torch.cat([torch.arange(s, s + m) for s, m in zip(starts, lengths)]).int().to(dev))
         proj = torch.randn(T, 2 * H * n + 2 * H * nv, device=dev).to(bf)

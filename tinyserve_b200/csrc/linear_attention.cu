@@ -15,13 +15,13 @@
 // projections, the gate and the result (float or bfloat16).
 //
 // One block per (request, head) walks the request's tokens of this step in order, a single
-// decoded token and a prompt portion of any length alike.  (A head of more than 128 value
-// columns is spread over several blocks of 128 columns; the output norm, which needs the whole
-// head, then runs as a kernel of its own on the 32-bit outputs.)  Thread (column c, row group g) keeps
-// rows [g R, (g + 1) R) of column c of the state in registers (R = key size / 4); the four
-// groups of a column are neighbouring lanes and add their shares of o_t by shuffles.  Tokens
-// are staged through shared memory sixteen at a time (rotary, factors and decays applied while
-// staging), and the output norm and gate run once per sixteen tokens on the staged outputs.
+// decoded token and a prompt portion of any length alike.  (A head with more value columns than
+// a block takes is spread over several blocks; the output norm, which needs the whole head, then
+// runs as a kernel of its own on the 32-bit outputs.)  A thread keeps a tile of up to 16 rows x 4
+// columns of the state in registers; the row groups of a column quad are neighbouring lanes and
+// add their shares of o_t by shuffles.  Tokens are staged through shared memory sixteen at a
+// time (rotary, factors and decays applied while staging), and the output norm and gate run
+// once per sixteen tokens on the staged outputs.
 //
 // Long portions are cut into segments of `seg_len` tokens that run side by side (a request of
 // 2,048 tokens and 8 heads alone would keep 8 of 148 SMs busy): the recurrence is linear in S, so
@@ -44,11 +44,24 @@ TS_DEFINE_LAST_ERROR()
 namespace {
 
 constexpr int DIM = TS_KEY_DIM;
-constexpr int GROUPS = 4;                 // row groups of a column
+// Row groups of a column: the smallest power of two that divides the key size and leaves a
+// thread at most 16 state rows (a thread keeps rows x COLS state elements in registers).
+constexpr int pick_groups() {
+  for (int g = 1; g <= 32; g *= 2)
+    if (DIM % g == 0 && DIM / g <= 16) return g;
+  return 0;
+}
+constexpr int GROUPS = pick_groups();
+static_assert(GROUPS > 0, "the key size must split into 1, 2, 4, ... 32 groups of at most 16 rows");
 constexpr int R = DIM / GROUPS;           // state rows of a thread
-constexpr int RP = R + 4;                 // padded length of a group's run in shared memory
+constexpr int COLS = 4;                   // state columns of a thread
+constexpr int RP = (R + 3) / 4 * 4 + 4;   // padded length of a group's run in shared memory (16-byte runs, spread over banks)
 constexpr int CHUNK = 16;                 // tokens staged at a time
-static_assert(DIM % GROUPS == 0 && DIM >= 4 && DIM <= 512, "key size must be a multiple of 4 up to 512");
+constexpr int MAX_THREADS = 256;
+#ifndef TS_SCAN_BLOCKS
+#define TS_SCAN_BLOCKS 2                  // blocks per SM that the register count is held to
+#endif
+constexpr int MAX_COLS = 256;             // value columns of a block at most (a whole head, where it fits)
 
 struct ScanParams {
   const void* q; const void* k; const void* v; const void* gate;
@@ -67,7 +80,7 @@ struct ScanParams {
   float* seg_state;                       // [B, H, segments, DIM, vdim]: local end states, then start states
   float* seg_decay;                       // [B, H, segments, DIM]: product of a segment's decays (per channel)
   int max_segments;
-  int cols, col_tiles;                    // value columns per block; blocks per head
+  int cols, col_tiles;                    // value columns per block (a multiple of COLS); blocks per head
   float* raw_out;                         // [T, H * vdim] 32-bit o_t before norm and gate (col_tiles > 1), else null
 };
 
@@ -75,10 +88,28 @@ enum { SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FROM_SEGMENT = 2 };
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-constexpr int MAX_THREADS = 512;
+// Ask for the 128-byte lines of `rows` runs of `bytes` bytes, `stride` bytes apart, to be brought
+// into L1: the staging of the next chunk then finds its operands there instead of waiting for L2
+// or HBM behind a barrier.  A hint only: nothing is read into registers and nothing waits.
+__device__ __forceinline__ void prefetch_rows(const void* first, long long stride, int bytes, int rows, int tid, int threads) {
+  const char* base = static_cast<const char*>(first);
+  const int lines = (bytes + 127) / 128 + 1;                  // (a run that starts inside a line touches one more)
+  for (int idx = tid; idx < rows * lines; idx += threads) {
+    const int row = idx / lines, at = (idx % lines) * 128;
+    if (at < bytes + 127) {
+      const char* ptr = base + (long long)row * stride + (at < bytes ? at : bytes - 1);
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
+    }
+  }
+}
 
+// Thread (column quad lc, row group g) keeps rows [g R, (g + 1) R) of columns [4 lc, 4 lc + 4) of
+// the block's columns: per token it reads R values each of q, k (and the decays) and four of v
+// from shared memory for 3 R x 4 multiply-adds, so the arithmetic, not shared memory, is what
+// it waits for.  The row groups of a column quad are neighbouring lanes and add their shares of
+// o_t by shuffles.
 template <typename T, bool PER_CHANNEL, int MODE>
-__global__ void __launch_bounds__(MAX_THREADS, 1) linear_attention_scan_kernel(ScanParams p) {
+__global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_scan_kernel(ScanParams p) {
   extern __shared__ float smem[];
   const int vdim = p.vdim, cols = p.cols;
   float* sq = smem;                                   // [CHUNK][GROUPS][RP]
@@ -98,27 +129,33 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) linear_attention_scan_kernel(S
   if (t1 <= t0) return;
   const bool last = t1 == request_end;
   if (MODE == SCAN_LOCAL && last) return;          // the last segment's end state is the output pass's
-  const int tid = threadIdx.x, lc = tid / GROUPS, c = col0 + lc, g = tid % GROUPS;
-  const bool owner = lc < cols && c < vdim;
+  const int tid = threadIdx.x, lc = tid / GROUPS, g = tid % GROUPS;
+  const int c = col0 + lc * COLS;                  // first of the thread's columns in the head
+  const bool in_block = lc * COLS < cols;
+  bool owns[COLS];
+#pragma unroll
+  for (int j = 0; j < COLS; ++j) owns[j] = in_block && c + j < vdim;
+  const bool quad = owns[COLS - 1] && vdim % 4 == 0;        // four columns, 16-byte aligned in every row
   const int slot = p.state_slots[b];
   float* S = p.state + (((size_t)slot * p.H + h) * DIM + (size_t)g * R) * vdim + c;
   const size_t seg_index = ((size_t)b * p.H + h) * p.max_segments + seg;
   float* seg_S = MODE == SCAN_WHOLE ? nullptr : p.seg_state + (seg_index * DIM + (size_t)g * R) * vdim + c;
-  float s[R];
+  float s[R][COLS];
   float dprod[PER_CHANNEL && MODE == SCAN_LOCAL ? R : 1];
   if (PER_CHANNEL && MODE == SCAN_LOCAL) {
 #pragma unroll
     for (int r = 0; r < R; ++r) dprod[r] = 1.f;
   }
-  if (MODE == SCAN_WHOLE && owner && !p.fresh[b]) {
+  const float* from = MODE == SCAN_WHOLE ? (p.fresh[b] ? nullptr : S) : (MODE == SCAN_FROM_SEGMENT ? seg_S : nullptr);
 #pragma unroll
-    for (int r = 0; r < R; ++r) s[r] = S[(size_t)r * vdim];
-  } else if (MODE == SCAN_FROM_SEGMENT && owner) {
+  for (int r = 0; r < R; ++r) {
+    if (from && quad) {
+      const float4 x = *reinterpret_cast<const float4*>(from + (size_t)r * vdim);
+      s[r][0] = x.x; s[r][1] = x.y; s[r][2] = x.z; s[r][3] = x.w;
+    } else {
 #pragma unroll
-    for (int r = 0; r < R; ++r) s[r] = seg_S[(size_t)r * vdim];
-  } else {
-#pragma unroll
-    for (int r = 0; r < R; ++r) s[r] = 0.f;
+      for (int j = 0; j < COLS; ++j) s[r][j] = from && owns[j] ? from[(size_t)r * vdim + j] : 0.f;
+    }
   }
   const float head_decay = PER_CHANNEL ? 1.f : p.decay[h];
   const T* q = static_cast<const T*>(p.q) + (size_t)h * DIM;
@@ -132,55 +169,96 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) linear_attention_scan_kernel(S
 
   for (int base = t0; base < t1; base += CHUNK) {
     const int n = min(CHUNK, t1 - base);
-    // stage q, k (rotary and factor applied), the decays and v
-    for (int idx = tid; idx < n * DIM; idx += blockDim.x) {
-      const int tok = idx / DIM, i = idx % DIM;
+    // stage q, k (rotary and factor applied), the decays and v.  The loads are read-only ones
+    // (what they read was finished before this kernel's wait returned), several in flight per
+    // thread: a chunk's staging would otherwise cost as much as its arithmetic
+    auto where = [](int tok, int i) { return (tok * GROUPS + i / R) * RP + i % R; };
+#pragma unroll 4
+    for (int idx = tid; idx < n * half; idx += blockDim.x) {       // a pair (j, j + half) per turn
+      const int tok = idx / half, j = idx % half;
       const size_t t = base + tok;
-      float qa = to_f32<T>(q[t * p.ldq + i]), ka = to_f32<T>(k[t * p.ldk + i]);
-      if (i < rot) {
-        const bool first = i < half;
-        const int j = first ? i : i - half, mate = first ? i + half : i - half;
-        const float qb = to_f32<T>(q[t * p.ldq + mate]), kb = to_f32<T>(k[t * p.ldk + mate]);
-        const size_t at = (size_t)p.positions[t] * half + j;
-        const float cs = p.cos[at], sn = p.sin[at];
-        qa = first ? qa * cs - qb * sn : qa * cs + qb * sn;
-        ka = first ? ka * cs - kb * sn : ka * cs + kb * sn;
+      const size_t at = (size_t)__ldg(p.positions + t) * half + j;
+      const float cs = __ldg(p.cos + at), sn = __ldg(p.sin + at);
+      const float ka = to_f32<T>(__ldg(k + t * p.ldk + j)), kb = to_f32<T>(__ldg(k + t * p.ldk + j + half));
+      sk[where(tok, j)] = (ka * cs - kb * sn) * p.k_scale;
+      sk[where(tok, j + half)] = (kb * cs + ka * sn) * p.k_scale;
+      if (MODE != SCAN_LOCAL) {
+        const float qa = to_f32<T>(__ldg(q + t * p.ldq + j)), qb = to_f32<T>(__ldg(q + t * p.ldq + j + half));
+        sq[where(tok, j)] = (qa * cs - qb * sn) * p.q_scale;
+        sq[where(tok, j + half)] = (qb * cs + qa * sn) * p.q_scale;
       }
-      const int where = (tok * GROUPS + i / R) * RP + i % R;
-      if (MODE != SCAN_LOCAL) sq[where] = qa * p.q_scale;
-      sk[where] = ka * p.k_scale;
-      if (PER_CHANNEL) sa[where] = expf(log_sigmoid(p.z[t * p.ldz + (size_t)h * DIM + i]) * p.inv_tau);
     }
+    const int plain = DIM - rot;
+#pragma unroll 4
+    for (int idx = tid; idx < n * plain; idx += blockDim.x) {      // the elements behind the rotary ones
+      const int tok = idx / plain, i = rot + idx % plain;
+      const size_t t = base + tok;
+      sk[where(tok, i)] = to_f32<T>(__ldg(k + t * p.ldk + i)) * p.k_scale;
+      if (MODE != SCAN_LOCAL) sq[where(tok, i)] = to_f32<T>(__ldg(q + t * p.ldq + i)) * p.q_scale;
+    }
+    if (PER_CHANNEL) {
+#pragma unroll 4
+      for (int idx = tid; idx < n * DIM; idx += blockDim.x) {
+        const int tok = idx / DIM, i = idx % DIM;
+        sa[where(tok, i)] = expf(log_sigmoid(__ldg(p.z + (size_t)(base + tok) * p.ldz + (size_t)h * DIM + i)) * p.inv_tau);
+      }
+    }
+#pragma unroll 4
     for (int idx = tid; idx < n * cols; idx += blockDim.x) {
       const int tok = idx / cols, i = idx % cols;
-      sv[tok * cols + i] = col0 + i < vdim ? to_f32<T>(v[(size_t)(base + tok) * p.ldv + col0 + i]) : 0.f;
+      sv[tok * cols + i] = col0 + i < vdim ? to_f32<T>(__ldg(v + (size_t)(base + tok) * p.ldv + col0 + i)) : 0.f;
     }
     __syncthreads();
-    {       // (threads beyond the columns run along with a value of zero: the shuffles need whole warps)
+    if (base + CHUNK < t1) {        // the next chunk's operands, on their way while this one is computed
+      const int m = min(CHUNK, t1 - base - CHUNK), threads = blockDim.x;
+      const size_t t = base + CHUNK;
+      prefetch_rows(k + t * p.ldk, p.ldk * (long long)sizeof(T), DIM * (int)sizeof(T), m, tid, threads);
+      prefetch_rows(v + t * p.ldv + col0, p.ldv * (long long)sizeof(T), min(cols, vdim - col0) * (int)sizeof(T), m, tid, threads);
+      if (PER_CHANNEL) prefetch_rows(p.z + t * p.ldz + (size_t)h * DIM, p.ldz * 4, DIM * 4, m, tid, threads);
+      if (MODE != SCAN_LOCAL) {
+        prefetch_rows(q + t * p.ldq, p.ldq * (long long)sizeof(T), DIM * (int)sizeof(T), m, tid, threads);
+        if (p.gate && !p.raw_out)
+          prefetch_rows(gate + t * p.ldg, p.ldg * (long long)sizeof(T), vdim * (int)sizeof(T), m, tid, threads);
+      }
+      if (half > 0) {
+        const size_t at = (size_t)__ldg(p.positions + t) * half;          // (a request's positions in a step are consecutive)
+        prefetch_rows(p.cos + at, half * 4, half * 4, m, tid, threads);
+        prefetch_rows(p.sin + at, half * 4, half * 4, m, tid, threads);
+      }
+    }
+    if (in_block) {       // (whole warps or none: cols is a multiple of 32 / GROUPS columns quads, see the launch)
       for (int tok = 0; tok < n; ++tok) {
         const float* qr = sq + (tok * GROUPS + g) * RP;
         const float* kr = sk + (tok * GROUPS + g) * RP;
         const float* ar = sa + (tok * GROUPS + g) * RP;
-        const float vv = owner ? sv[tok * cols + lc] : 0.f;
-        if (MODE == SCAN_LOCAL) {
-#pragma unroll
-          for (int r = 0; r < R; ++r) {
-            const float a = PER_CHANNEL ? ar[r] : head_decay;
-            s[r] = fmaf(a, s[r], kr[r] * vv);
-            if (PER_CHANNEL && c == 0) dprod[r] *= a;      // (column 0 of the head: one block's first four threads)
-          }
-          continue;
-        }
-        float acc = 0.f;
+        const float4 v4 = *reinterpret_cast<const float4*>(sv + tok * cols + lc * COLS);
+        const float vv[COLS] = {v4.x, v4.y, v4.z, v4.w};
+        float acc[COLS] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           const float a = PER_CHANNEL ? ar[r] : head_decay;
-          s[r] = fmaf(a, s[r], kr[r] * vv);
-          acc = fmaf(s[r], qr[r], acc);
+          const float kk = kr[r];
+          if (PER_CHANNEL && MODE == SCAN_LOCAL && c == 0) dprod[r] *= a;      // (column 0 of the head: one quad's threads)
+          if (MODE == SCAN_LOCAL) {
+#pragma unroll
+            for (int j = 0; j < COLS; ++j) s[r][j] = fmaf(a, s[r][j], kk * vv[j]);
+          } else {
+            const float qq = qr[r];
+#pragma unroll
+            for (int j = 0; j < COLS; ++j) {
+              s[r][j] = fmaf(a, s[r][j], kk * vv[j]);
+              acc[j] = fmaf(s[r][j], qq, acc[j]);
+            }
+          }
         }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        if (g == 0 && owner) so[tok * cols + lc] = acc;
+        if (MODE != SCAN_LOCAL) {
+#pragma unroll
+          for (int o = 1; o < GROUPS; o <<= 1) {
+#pragma unroll
+            for (int j = 0; j < COLS; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+          }
+          if (g == 0) *reinterpret_cast<float4*>(so + tok * cols + lc * COLS) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        }
       }
     }
     __syncthreads();
@@ -208,20 +286,22 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) linear_attention_scan_kernel(S
     }
     if constexpr (MODE != SCAN_LOCAL) __syncthreads();
   }
-  if (MODE == SCAN_LOCAL) {
-    if (owner) {
+  float* to = MODE == SCAN_LOCAL ? seg_S : ((MODE == SCAN_WHOLE || last) ? S : nullptr);
+  if (to) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) seg_S[(size_t)r * vdim] = s[r];
-    }
-    if (PER_CHANNEL && c == 0) {
+    for (int r = 0; r < R; ++r) {
+      if (quad) {
+        *reinterpret_cast<float4*>(to + (size_t)r * vdim) = make_float4(s[r][0], s[r][1], s[r][2], s[r][3]);
+      } else {
 #pragma unroll
-      for (int r = 0; r < R; ++r) p.seg_decay[seg_index * DIM + g * R + r] = dprod[r];
+        for (int j = 0; j < COLS; ++j)
+          if (owns[j]) to[(size_t)r * vdim + j] = s[r][j];
+      }
     }
-    return;
   }
-  if (owner && (MODE == SCAN_WHOLE || last)) {
+  if (PER_CHANNEL && MODE == SCAN_LOCAL && c == 0 && in_block) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) S[(size_t)r * vdim] = s[r];
+    for (int r = 0; r < R; ++r) p.seg_decay[seg_index * DIM + g * R + r] = dprod[r];
   }
 }
 
@@ -273,18 +353,28 @@ __global__ void linear_attention_combine_kernel(ScanParams p) {
     for (int i = 0; i < p.seg_len; ++i) head_decay *= d;
   }
   const size_t first = ((size_t)b * p.H + h) * p.max_segments;
-  for (int seg = 0; seg < segments; ++seg) {
-    float* at = p.seg_state + (first + seg) * DIM * p.vdim + e;
-    const float local = seg + 1 < segments ? *at : 0.f;
-    *at = s;
-    const float d = PER_CHANNEL ? (seg + 1 < segments ? p.seg_decay[(first + seg) * DIM + row] : 0.f) : head_decay;
-    s = fmaf(d, s, local);
+  // eight segments' loads at a time, then their chain of multiply-adds: the loads do not wait for one another
+  constexpr int BATCH = 8;
+  for (int seg0 = 0; seg0 < segments; seg0 += BATCH) {
+    float local[BATCH], d[BATCH];
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {
+      const int seg = seg0 + j;
+      const bool inner = seg + 1 < segments;       // (the last segment left no local state: the output pass makes the request's new one)
+      local[j] = inner ? p.seg_state[(first + seg) * DIM * p.vdim + e] : 0.f;
+      d[j] = PER_CHANNEL ? (inner ? p.seg_decay[(first + seg) * DIM + row] : 0.f) : head_decay;
+    }
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {
+      if (seg0 + j < segments) p.seg_state[(first + seg0 + j) * DIM * p.vdim + e] = s;
+      s = fmaf(d[j], s, local[j]);
+    }
   }
 }
 
 template <typename T, bool PER_CHANNEL, int MODE>
 int launch_scan_mode(const ScanParams& p, int num_requests, int segments, cudaStream_t stream) {
-  const int threads = (p.cols * GROUPS + 31) / 32 * 32;
+  const int threads = p.cols / COLS * GROUPS;       // a multiple of 32: see the choice of cols
   const size_t smem = ((size_t)(PER_CHANNEL ? 3 : 2) * CHUNK * GROUPS * RP + 2 * (size_t)CHUNK * p.cols) * sizeof(float);
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
@@ -319,6 +409,21 @@ int launch_scan(const ScanParams& p, int num_requests, int num_tokens, cudaStrea
 
 TS_EXPORT int ts_linear_attention_key_dim() { return DIM; }
 
+// value columns of a block: whole warps of column quads (32 / GROUPS quads each), a whole head where it fits
+static int block_columns(int vdim) {
+  const int step = COLS * (GROUPS >= 32 ? 1 : 32 / GROUPS);
+  const int most = MAX_COLS < COLS * MAX_THREADS / GROUPS ? MAX_COLS : COLS * MAX_THREADS / GROUPS;
+  const int padded = (vdim + step - 1) / step * step;
+  return padded <= most ? padded : most / step * step;
+}
+
+// blocks that a head of `vdim` value columns is spread over (more than one: the caller brings a
+// 32-bit scratch [T, H * vdim] for the outputs before their norm)
+TS_EXPORT int ts_linear_attention_column_tiles(int vdim) {
+  const int cols = block_columns(vdim);
+  return (vdim + cols - 1) / cols;
+}
+
 TS_EXPORT int ts_linear_attention(int dtype, const void* q, long long ldq, const void* k, long long ldk, const void* v,
                                   long long ldv, const void* gate, long long ldg, const float* z, long long ldz,
                                   float tau, const float* decay, const int* positions, const float* cos,
@@ -328,11 +433,11 @@ TS_EXPORT int ts_linear_attention(int dtype, const void* q, long long ldq, const
                                   int H, int vdim, int seg_len, float* seg_state, float* seg_decay, int max_segments,
                                   int num_tokens, float* raw_out, cudaStream_t stream) {
   TS_REQUIRE(num_requests > 0 && H > 0 && vdim > 0, "linear_attention: empty input");
-  const int cols = vdim < MAX_THREADS / GROUPS ? vdim : MAX_THREADS / GROUPS;
+  const int cols = block_columns(vdim);
   const int col_tiles = (vdim + cols - 1) / cols;
   TS_REQUIRE((col_tiles > 1) == (raw_out != nullptr) && num_tokens > 0,
              "linear_attention: heads of more than %d value columns come with a 32-bit scratch for their outputs, others without",
-             MAX_THREADS / GROUPS);
+             cols);
   TS_REQUIRE((z != nullptr) != (decay != nullptr), "linear_attention: either per-channel logits or per-head decays");
   TS_REQUIRE(z == nullptr || tau > 0.f, "linear_attention: tau must be positive");
   TS_REQUIRE(rotary_dim >= 0 && rotary_dim <= DIM && rotary_dim % 2 == 0, "linear_attention: rotary_dim %d does not fit key size %d", rotary_dim, DIM);

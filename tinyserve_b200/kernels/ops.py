@@ -1224,14 +1224,22 @@ def head_gate(attn, gate, vdim):
 
 # ----------------------------------------------------------------------------- linear attention with a matrix state
 LINEAR_ATTENTION_MAX_VALUE_DIM = 4096
-#: value columns of a head that one block of the scan takes; wider heads are spread over several
-#: blocks and their output norm runs as a kernel of its own
-LINEAR_ATTENTION_BLOCK_COLUMNS = 128
 #: a step whose longest portion has at least LINEAR_ATTENTION_SEGMENT_MIN tokens cuts its portions
-#: into segments of LINEAR_ATTENTION_SEGMENT tokens that run side by side (three launches instead
-#: of one: local states, their combination, outputs)
-LINEAR_ATTENTION_SEGMENT = 128
+#: into segments that run side by side (three launches instead of one: local states, their
+#: combination, outputs); the segments are as long as lets the longest portion's blocks fill the
+#: SMs once (two blocks per SM), a multiple of 16 tokens and at least LINEAR_ATTENTION_SEGMENT
+LINEAR_ATTENTION_SEGMENT = 64
 LINEAR_ATTENTION_SEGMENT_MIN = 256
+
+
+def linear_attention_segment(longest: int, blocks_per_segment: int) -> int:
+    """Tokens per segment for a step whose longest portion has ``longest`` tokens and launches
+    ``blocks_per_segment`` blocks (heads x column tiles) per segment; 0: one segment, one launch."""
+    if longest < LINEAR_ATTENTION_SEGMENT_MIN:
+        return 0
+    segments = max(1, 2 * num_sms() // max(1, blocks_per_segment))
+    length = max(LINEAR_ATTENTION_SEGMENT, -(-longest // segments))
+    return -(-length // 16) * 16
 
 
 def _linear_attention(key_dim: int):
@@ -1265,8 +1273,12 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
     out = torch.empty(T, H * value_dim, dtype=out_dtype, device=q.device)
     zp, zld = _columns(decay_logits) if decay_logits is not None else (c_void_p(0), c_longlong(0))
     gp, gld = _columns(gate) if gate is not None else (c_void_p(0), c_longlong(0))
+    lib = _linear_attention(key_dim)
+    # a head of more value columns than a block takes: its output norm runs as a kernel of its own
+    tiles = lib.ts_linear_attention_column_tiles(c_int(value_dim))
+    wide = tiles > 1
     if segment is None:
-        seg_len = LINEAR_ATTENTION_SEGMENT if getattr(ctx, "max_q_len", 0) >= LINEAR_ATTENTION_SEGMENT_MIN else 0
+        seg_len = linear_attention_segment(getattr(ctx, "max_q_len", 0), H * tiles)
     else:
         seg_len = int(segment)
     max_segments, seg_state, seg_decay = 0, None, None
@@ -1275,9 +1287,7 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
         seg_state = torch.empty(ctx.num_requests * H * max_segments * key_dim * value_dim, dtype=torch.float32, device=q.device)
         if decay_logits is not None:
             seg_decay = torch.empty(ctx.num_requests * H * max_segments * key_dim, dtype=torch.float32, device=q.device)
-    wide = value_dim > LINEAR_ATTENTION_BLOCK_COLUMNS
     raw = torch.empty(T, H * value_dim, dtype=torch.float32, device=q.device) if wide else None
-    lib = _linear_attention(key_dim)
     _check(lib, lib.ts_linear_attention(
         c_int(_dt(q)), *_columns(q), *_columns(k), *_columns(v), gp, gld, zp, zld, c_float(tau), _ptr(decay),
         _ptr(ctx.positions), _ptr(rotary.cos if rotary is not None else None),
