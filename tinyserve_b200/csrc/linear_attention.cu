@@ -141,11 +141,9 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
   const size_t seg_index = ((size_t)b * p.H + h) * p.max_segments + seg;
   float* seg_S = MODE == SCAN_WHOLE ? nullptr : p.seg_state + (seg_index * DIM + (size_t)g * R) * vdim + c;
   float s[R][COLS];
-  float dprod[PER_CHANNEL && MODE == SCAN_LOCAL ? R : 1];
-  if (PER_CHANNEL && MODE == SCAN_LOCAL) {
+  float w[PER_CHANNEL && MODE == SCAN_LOCAL ? R : 1];      // local pass: product of the decays behind the current token
 #pragma unroll
-    for (int r = 0; r < R; ++r) dprod[r] = 1.f;
-  }
+  for (int r = 0; r < (PER_CHANNEL && MODE == SCAN_LOCAL ? R : 1); ++r) w[r] = 1.f;
   const float* from = MODE == SCAN_WHOLE ? (p.fresh[b] ? nullptr : S) : (MODE == SCAN_FROM_SEGMENT ? seg_S : nullptr);
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -167,7 +165,13 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
   VecParam nw{p.norm_weight, p.norm_weight_is_f32};
   const int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
 
-  for (int base = t0; base < t1; base += CHUNK) {
+  // The local pass walks its segment backwards: with w_t the product of the decays behind token t,
+  // the end state from zero is sum_t (w_t k_t) v_t^T, one multiply-add per state element and token
+  // (the recurrence costs two), and w ends as the product of all the segment's decays.
+  const int chunks = (t1 - t0 + CHUNK - 1) / CHUNK;
+  for (int turn = 0; turn < chunks; ++turn) {
+    const int base = t0 + (MODE == SCAN_LOCAL ? chunks - 1 - turn : turn) * CHUNK;
+    const int next = MODE == SCAN_LOCAL ? base - CHUNK : base + CHUNK;
     const int n = min(CHUNK, t1 - base);
     // stage q, k (rotary and factor applied), the decays and v.  The loads are read-only ones
     // (what they read was finished before this kernel's wait returned), several in flight per
@@ -209,9 +213,9 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       sv[tok * cols + i] = col0 + i < vdim ? to_f32<T>(__ldg(v + (size_t)(base + tok) * p.ldv + col0 + i)) : 0.f;
     }
     __syncthreads();
-    if (base + CHUNK < t1) {        // the next chunk's operands, on their way while this one is computed
-      const int m = min(CHUNK, t1 - base - CHUNK), threads = blockDim.x;
-      const size_t t = base + CHUNK;
+    if (turn + 1 < chunks) {        // the next chunk's operands, on their way while this one is computed
+      const int m = min(CHUNK, t1 - next), threads = blockDim.x;
+      const size_t t = next;
       prefetch_rows(k + t * p.ldk, p.ldk * (long long)sizeof(T), DIM * (int)sizeof(T), m, tid, threads);
       prefetch_rows(v + t * p.ldv + col0, p.ldv * (long long)sizeof(T), min(cols, vdim - col0) * (int)sizeof(T), m, tid, threads);
       if (PER_CHANNEL) prefetch_rows(p.z + t * p.ldz + (size_t)h * DIM, p.ldz * 4, DIM * 4, m, tid, threads);
@@ -227,6 +231,22 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       }
     }
     if (in_block) {       // (whole warps or none: cols is a multiple of 32 / GROUPS columns quads, see the launch)
+      if constexpr (MODE == SCAN_LOCAL) {
+        for (int tok = n - 1; tok >= 0; --tok) {
+          const float* kr = sk + (tok * GROUPS + g) * RP;
+          const float* ar = sa + (tok * GROUPS + g) * RP;
+          const float4 v4 = *reinterpret_cast<const float4*>(sv + tok * cols + lc * COLS);
+          const float vv[COLS] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const float kw = kr[r] * (PER_CHANNEL ? w[r] : w[0]);
+#pragma unroll
+            for (int j = 0; j < COLS; ++j) s[r][j] = fmaf(kw, vv[j], s[r][j]);
+            if (PER_CHANNEL) w[r] *= ar[r];
+          }
+          if (!PER_CHANNEL) w[0] *= head_decay;
+        }
+      } else
       for (int tok = 0; tok < n; ++tok) {
         const float* qr = sq + (tok * GROUPS + g) * RP;
         const float* kr = sk + (tok * GROUPS + g) * RP;
@@ -237,28 +257,19 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           const float a = PER_CHANNEL ? ar[r] : head_decay;
-          const float kk = kr[r];
-          if (PER_CHANNEL && MODE == SCAN_LOCAL && c == 0) dprod[r] *= a;      // (column 0 of the head: one quad's threads)
-          if (MODE == SCAN_LOCAL) {
+          const float kk = kr[r], qq = qr[r];
 #pragma unroll
-            for (int j = 0; j < COLS; ++j) s[r][j] = fmaf(a, s[r][j], kk * vv[j]);
-          } else {
-            const float qq = qr[r];
-#pragma unroll
-            for (int j = 0; j < COLS; ++j) {
-              s[r][j] = fmaf(a, s[r][j], kk * vv[j]);
-              acc[j] = fmaf(s[r][j], qq, acc[j]);
-            }
+          for (int j = 0; j < COLS; ++j) {
+            s[r][j] = fmaf(a, s[r][j], kk * vv[j]);
+            acc[j] = fmaf(s[r][j], qq, acc[j]);
           }
         }
-        if (MODE != SCAN_LOCAL) {
 #pragma unroll
-          for (int o = 1; o < GROUPS; o <<= 1) {
+        for (int o = 1; o < GROUPS; o <<= 1) {
 #pragma unroll
-            for (int j = 0; j < COLS; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
-          }
-          if (g == 0) *reinterpret_cast<float4*>(so + tok * cols + lc * COLS) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+          for (int j = 0; j < COLS; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
         }
+        if (g == 0) *reinterpret_cast<float4*>(so + tok * cols + lc * COLS) = make_float4(acc[0], acc[1], acc[2], acc[3]);
       }
     }
     __syncthreads();
@@ -301,7 +312,7 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
   }
   if (PER_CHANNEL && MODE == SCAN_LOCAL && c == 0 && in_block) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) p.seg_decay[seg_index * DIM + g * R + r] = dprod[r];
+    for (int r = 0; r < R; ++r) p.seg_decay[seg_index * DIM + g * R + r] = w[PER_CHANNEL && MODE == SCAN_LOCAL ? r : 0];
   }
 }
 

@@ -496,8 +496,9 @@ def _sampler():
     return build.load_unit("sampler.cu")
 
 
-def units_for(head_dims) -> list:
-    """The (source, defines) units a model with these head sizes needs."""
+def units_for(head_dims, key_dims=()) -> list:
+    """The (source, defines) units a model with these attention head sizes, and these key sizes of
+    its matrix-state mixers, needs."""
     units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("gemm_tcgen05.cu", {}), ("gemm_pair_tcgen05.cu", {}),
              ("sampler.cu", {})]
     units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
@@ -505,6 +506,7 @@ def units_for(head_dims) -> list:
               if d <= MMA_MAX_HEAD_DIM]
     units += [("attention_tcgen05.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
               if d in TCGEN05_HEAD_DIMS]
+    units += [("linear_attention.cu", {"TS_KEY_DIM": d}) for d in sorted(set(key_dims))]
     return units
 
 
