@@ -342,7 +342,7 @@ def dudatar_shapes(width):
     heads, ff, vocab = width // 128, width * 11 // 4, 32768
     rot = lambda dims: {"dims": dims, "base": 1e6}
     gla = {"type": "gla", "mlp": {"kind": "dense", "ff": ff},
-           "mixer": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0, "rank": 16}}
+           "mixer": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 8.0, "rank": 32}}
     par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
         "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot(64)},
         "right": {"heads": heads // 2, "dim": 128, "vdim": 256, "rot": rot(128),
@@ -398,7 +398,7 @@ def kernel_table(width, peaks):
         flops = 4.0 * T * H * n * nv
         nbytes = T * (2 * H * n + 3 * H * nv) * 2 + 2 * B * H * n * nv * 4
         for kind, kw in (("retention", dict(decay=decay, k_scale=n ** -0.5)),
-                         ("gla", dict(decay_logits=z, tau=16.0, q_scale=n ** -0.5, norm_weight=w))):
+                         ("gla", dict(decay_logits=z, tau=8.0, q_scale=n ** -0.5, norm_weight=w))):
             us = _time_us(lambda: ops.linear_attention(q, k, v, g, state, ctx, H, n, nv, bf, eps=1e-5, **kw))
             extra = T * H * n * 4 if kind == "gla" else 0
             roof = max((nbytes + extra) / (peaks["hbm_gbs"] * 1e3), flops / (fma_tflops * 1e6))

@@ -29,8 +29,8 @@ DUDATAR_TINY = {
         "layers": [
             {"type": "gla", "mlp": {"kind": "dense", "ff": 160}, "mixer": {"heads": 3, "dim": 20, "vdim": 24, "tau": 1.0, "rank": 12}},
             {"type": "parallel", "mlp": {"kind": "dense", "ff": 72}, "mixer": {
-                "left": {"heads": 2, "kv_heads": 1, "dim": 48, "vdim": 48, "scale": 0.3, "rot": _rot(24, 5e5)},
-                "right": {"heads": 3, "dim": 16, "vdim": 32, "decay": [0.5, 0.95, 0.999], "rot": _rot(16, 1e6)}}},
+                "left": {"heads": 2, "kv_heads": 1, "dim": 48, "vdim": 48, "scale": 0.3, "rot": _rot(24, 2e5)},
+                "right": {"heads": 3, "dim": 16, "vdim": 32, "decay": [0.5, 0.95, 0.999], "rot": _rot(16, 3e6)}}},
             {"type": "gla", "mlp": {"kind": "dense", "ff": 160}, "mixer": {"heads": 1, "dim": 32, "vdim": 64, "tau": 8.0, "rank": 4}},
         ]},
     # head sizes of 64 (the tensor-core attention kernels), a loop of one pass in the middle, a
@@ -42,7 +42,7 @@ DUDATAR_TINY = {
             {"type": "parallel", "mlp": {"kind": "dense", "ff": 192}, "mixer": {
                 "left": {"heads": 8, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.25, "rot": _rot(32, 1e4)},
                 "right": {"heads": 2, "dim": 64, "vdim": 128, "decay": [0.96875, 0.998], "rot": _rot(64, 1e4)}}},
-            {"type": "gla", "mlp": {"kind": "dense", "ff": 192}, "mixer": {"heads": 2, "dim": 64, "vdim": 64, "tau": 16.0, "rank": 16}},
+            {"type": "gla", "mlp": {"kind": "dense", "ff": 192}, "mixer": {"heads": 2, "dim": 64, "vdim": 64, "tau": 12.0, "rank": 24}},
             {"type": "parallel", "mlp": {"kind": "dense", "ff": 256}, "mixer": {
                 "left": {"heads": 4, "kv_heads": 4, "dim": 64, "vdim": 32, "scale": 0.125, "rot": _rot(64, 1e6)},
                 "right": {"heads": 4, "dim": 32, "vdim": 32, "decay": [0.9, 0.99, 0.999, 0.9999], "rot": _rot(16, 1e4)}}},

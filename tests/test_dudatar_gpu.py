@@ -142,7 +142,7 @@ def test_rotation_unit_norm_and_padded_cache_write(dtype, tol, H, G, n, nv, rot)
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
 @pytest.mark.parametrize("kind", ["per_head", "per_channel"])
-@pytest.mark.parametrize("H,n,nv", [(2, 16, 32), (3, 20, 24), (1, 64, 128), (2, 16, 160)])
+@pytest.mark.parametrize("H,n,nv", [(2, 16, 32), (3, 20, 24), (1, 64, 128), (2, 16, 160), (2, 36, 30)])
 @pytest.mark.parametrize("segment", [0, 16])
 def test_matrix_state_scan_in_portions_from_and_to_slots(dtype, tol, kind, H, n, nv, segment):
     """Three requests of unequal length, cut into steps of unequal portions (one token, two,
@@ -340,13 +340,16 @@ def test_far_keys_and_long_memories(dtype, tmp_path):
     short = plain.logits(cfg, weights, ids[60:])                 # the same tail without what lies far back
     assert (short[-1] - ref["far"][-1]).abs().max() > 0.05 * ref["far"].abs().max(), "the far tokens matter here"
     model = {"name": "Zsharp", "folder": sharp, "cfg": cfg, "requests": reqs, "ref": ref}
-    # (sums over hundreds of tokens that hardly decay, and a softmax that leans on single keys:
-    # twice the rounding of the models above; measured 8.8e-5 and 2.6e-5 in float32)
-    check(model, dtype, schedule_whole(reqs), tmp_path / "whole", slack=2.0)
-    check(model, dtype, schedule_tail_decode(reqs, 40), tmp_path / "tail", slack=2.0)
-    check(model, dtype, schedule_portions(reqs, sizes=(63, 2, 1, 64, 5, 16, 15)), tmp_path / "portions", slack=2.0)
+    # (sums over hundreds of tokens that hardly decay, and a softmax that leans on single keys: twice
+    # the rounding of the models above in float32, measured 8.8e-5 and 2.6e-5; three times in bfloat16,
+    # measured 5.0e-1 and 1.3e-1 of the largest logit, where leaving out what lies far back moves the
+    # last logits by 1.3 times the largest logit)
+    slack = 2.0 if dtype == "float32" else 3.0
+    check(model, dtype, schedule_whole(reqs), tmp_path / "whole", slack=slack)
+    check(model, dtype, schedule_tail_decode(reqs, 40), tmp_path / "tail", slack=slack)
+    check(model, dtype, schedule_portions(reqs, sizes=(63, 2, 1, 64, 5, 16, 15)), tmp_path / "portions", slack=slack)
     check(model, dtype, schedule_mixed({**reqs, "farx": ids, "nearx": ids[:70]}, max_live=3, seed=5), tmp_path / "mixed",
-          slack=2.0, max_live=3)
+          slack=slack, max_live=3)
 
 
 # ----------------------------------------------------------------------------- the entry point

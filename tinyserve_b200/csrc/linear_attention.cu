@@ -36,7 +36,7 @@
 #include "common.cuh"
 
 #ifndef TS_KEY_DIM
-#error "compile with -DTS_KEY_DIM=<key size, a multiple of 4>"
+#error "compile with -DTS_KEY_DIM=<key size>"
 #endif
 
 TS_DEFINE_LAST_ERROR()
@@ -45,14 +45,16 @@ namespace {
 
 constexpr int DIM = TS_KEY_DIM;
 // Row groups of a column: the smallest power of two that divides the key size and leaves a
-// thread at most 16 state rows (a thread keeps rows x COLS state elements in registers).
+// thread at most 16 state rows (a thread keeps rows x COLS state elements in registers); key
+// sizes that no power of two cuts that small get up to 32, then up to 64 rows a thread.
 constexpr int pick_groups() {
-  for (int g = 1; g <= 32; g *= 2)
-    if (DIM % g == 0 && DIM / g <= 16) return g;
+  for (int most = 16; most <= 64; most *= 2)
+    for (int g = 1; g <= 32; g *= 2)
+      if (DIM % g == 0 && DIM / g <= most) return g;
   return 0;
 }
 constexpr int GROUPS = pick_groups();
-static_assert(GROUPS > 0, "the key size must split into 1, 2, 4, ... 32 groups of at most 16 rows");
+static_assert(GROUPS > 0, "the key size must split into 1, 2, 4, ... 32 groups of at most 64 rows");
 constexpr int R = DIM / GROUPS;           // state rows of a thread
 constexpr int COLS = 4;                   // state columns of a thread
 constexpr int RP = (R + 3) / 4 * 4 + 4;   // padded length of a group's run in shared memory (16-byte runs, spread over banks)

@@ -1244,9 +1244,16 @@ def linear_attention_segment(longest: int, blocks_per_segment: int) -> int:
     return -(-length // 16) * 16
 
 
+def linear_attention_supports(key_dim: int) -> bool:
+    """Key sizes the scan is built for: those that 1, 2, 4, ... or 32 row groups cut into at most
+    64 rows each."""
+    return 0 < key_dim <= 2048 and any(key_dim % g == 0 and key_dim // g <= 64 for g in (1, 2, 4, 8, 16, 32))
+
+
 def _linear_attention(key_dim: int):
-    if key_dim % 4 or not 4 <= key_dim <= 512:
-        raise ValueError(f"key size {key_dim} is not supported: linear attention takes multiples of 4 up to 512")
+    if not linear_attention_supports(key_dim):
+        raise ValueError(f"key size {key_dim} is not supported: linear attention takes key sizes that split into "
+                         f"1, 2, 4, ... or 32 groups of at most 64 rows")
     return build.load_unit("linear_attention.cu", {"TS_KEY_DIM": key_dim})
 
 

@@ -35,9 +35,8 @@ class MatrixStateMixer(Mixer):
         self.names = dict(DEFAULT_NAMES, **(names or {}))
         self.hidden_size, self.num_heads = hidden_size, num_heads
         self.key_dim, self.value_dim, self.eps = key_dim, value_dim, float(eps)
-        if key_dim % 4 or value_dim > ops.LINEAR_ATTENTION_MAX_VALUE_DIM:
-            raise ValueError(f"linear attention takes key sizes that are multiples of 4 and value sizes up to "
-                             f"{ops.LINEAR_ATTENTION_MAX_VALUE_DIM}, got {key_dim} and {value_dim}")
+        if not ops.linear_attention_supports(key_dim) or not 0 < value_dim <= ops.LINEAR_ATTENTION_MAX_VALUE_DIM:
+            raise ValueError(f"linear attention: key size {key_dim} or value size {value_dim} is not supported")
         self.qk_size, self.v_size = num_heads * key_dim, num_heads * value_dim
 
     def _projection_rows(self):
