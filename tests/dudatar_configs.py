@@ -64,3 +64,41 @@ def dudatar_config(name: str):
 def make_dudatar_dir(folder, name: str, seed: int = 0) -> str:
     from tinyserve_b200.weights import write_random_model
     return write_random_model(dudatar_config(name), str(folder), seed=seed)
+
+
+def random_dudatar_config_dict(seed: int) -> dict:
+    """A configuration drawn from a seed: sizes that are no power of two and no multiple of 16
+    among them, any order of layer kinds, a loop anywhere or none, layers without feed-forward."""
+    import random
+    r = random.Random(seed)
+    even = lambda lo, hi: 2 * r.randint(lo // 2, hi // 2)
+    width = 8 * r.randint(4, 14)
+
+    def rot(dim):
+        return _rot(r.choice([0, dim, even(2, dim)]), r.choice([100.0, 1e4, 7e5]))
+
+    def layer():
+        mlp = None if r.random() < 0.25 else {"kind": "dense", "ff": 8 * r.randint(3, 20)}
+        if r.random() < 0.5:
+            dim = r.choice([4, 8, 12, 20, 24, 36, 40, 64])
+            return {"type": "gla", "mlp": mlp, "mixer": {"heads": r.randint(1, 5), "dim": dim, "vdim": r.choice([6, 10, 16, 24, 30, 48, 72]),
+                                                        "tau": r.choice([1.0, 2.5, 16.0]), "rank": r.choice([3, 8, 12, 16])}}
+        kv = r.randint(1, 3)
+        ldim = even(8, 72)
+        rdim = r.choice([4, 8, 12, 20, 24, 36, 40, 64])
+        heads = r.randint(1, 4)
+        return {"type": "parallel", "mlp": mlp, "mixer": {
+            "left": {"heads": kv * r.randint(1, 3), "kv_heads": kv, "dim": ldim, "vdim": r.choice([8, 16, 24, 40, 64, 80]),
+                     "scale": r.choice([0.1, ldim ** -0.5, 0.4]), "rot": rot(ldim)},
+            "right": {"heads": heads, "dim": rdim, "vdim": r.choice([6, 10, 16, 24, 30, 48, 72]),
+                      "decay": [round(1.0 - 2.0 ** -r.uniform(1, 9), 6) for _ in range(heads)], "rot": rot(rdim)}}}
+
+    layers = [layer() for _ in range(r.randint(1, 4))]
+    raw = {"architecture": "Dudatar", "vocab": r.randint(50, 400), "width": width, "norm": {"eps": r.choice([1e-6, 1e-5, 1e-4])},
+           "layers": layers}
+    if r.random() < 0.7:
+        start = r.randint(0, len(layers) - 1)
+        raw["loop"] = {"start": start, "stop": r.randint(start + 1, len(layers)), "times": r.randint(1, 3)}
+    if r.random() < 0.7:
+        raw["logit_softcap"] = r.choice([0.3, 1.0, 25.0])
+    return raw

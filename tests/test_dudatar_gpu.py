@@ -11,7 +11,7 @@ import torch
 from safetensors.torch import load_file, save_file
 
 import plain_dudatar as plain
-from dudatar_configs import DUDATAR_TINY, dudatar_config, make_dudatar_dir
+from dudatar_configs import DUDATAR_TINY, dudatar_config, make_dudatar_dir, random_dudatar_config_dict
 from helpers import (collect_logits, lines_of, max_live_tokens, random_ids, schedule_mixed, schedule_portions,
                      schedule_tail_decode, schedule_whole)
 
@@ -300,6 +300,24 @@ def test_batch_of_unequal_requests_equals_each_alone(model, tmp_path):
         # (the attention kernel cuts a request's keys into ranges by how full the batch is: the
         # order of its sums, not what is summed, depends on the batch)
         assert (a[rid] - b[rid]).abs().max() <= 1e-5 * b[rid].abs().max()
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_drawn_configurations(seed, tmp_path):
+    """Configurations drawn from a seed (odd head sizes, head counts, ranks, loops, orders): whole
+    prompts, portions and a mixed batch in 32-bit against the plain implementation."""
+    from tinyserve_b200.config import config_from_dict
+    from tinyserve_b200.weights import write_random_model
+    raw = random_dudatar_config_dict(seed)
+    folder = write_random_model(config_from_dict(raw), str(tmp_path / "model"), seed=seed)
+    cfg, weights = plain.load_folder(folder)
+    reqs = {f"r{i}": random_ids(cfg["vocab"], n, seed=700 + 10 * seed + i) for i, n in enumerate((37, 5, 66, 1))}
+    ref = {rid: plain.logits(cfg, weights, ids) for rid, ids in reqs.items()}
+    model = {"name": "X", "folder": folder, "cfg": cfg, "requests": reqs, "ref": ref}
+    check(model, "float32", schedule_whole(reqs), tmp_path / "whole", slack=2.0)
+    check(model, "float32", schedule_portions(reqs, sizes=(17, 2, 16, 1, 3)), tmp_path / "portions", slack=2.0)
+    check(model, "float32", schedule_mixed(reqs, max_live=3, seed=seed), tmp_path / "mixed", slack=2.0, max_live=3)
+    check(model, "bfloat16", schedule_mixed(reqs, max_live=3, seed=seed), tmp_path / "mixed16", slack=2.0, max_live=3)
 
 
 # ----------------------------------------------------------------------------- weights that show a fault
