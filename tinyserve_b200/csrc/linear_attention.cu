@@ -59,9 +59,9 @@ constexpr int R = DIM / GROUPS;           // state rows of a thread
 constexpr int COLS = 4;                   // state columns of a thread
 constexpr int RP = (R + 3) / 4 * 4 + 4;   // padded length of a group's run in shared memory (16-byte runs, spread over banks)
 constexpr int CHUNK = 16;                 // tokens staged at a time
-constexpr int MAX_THREADS = 256;
+constexpr int MAX_THREADS = 512;
 #ifndef TS_SCAN_BLOCKS
-#define TS_SCAN_BLOCKS 2                  // blocks per SM that the register count is held to
+#define TS_SCAN_BLOCKS 1                  // blocks per SM that the register count is held to
 #endif
 constexpr int MAX_COLS = 256;             // value columns of a block at most (a whole head, where it fits)
 
@@ -93,16 +93,14 @@ __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - l
 // Ask for the 128-byte lines of `rows` runs of `bytes` bytes, `stride` bytes apart, to be brought
 // into L1: the staging of the next chunk then finds its operands there instead of waiting for L2
 // or HBM behind a barrier.  A hint only: nothing is read into registers and nothing waits.
-__device__ __forceinline__ void prefetch_rows(const void* first, long long stride, int bytes, int rows, int tid, int threads) {
+__device__ __forceinline__ void prefetch_rows(const void* first, long long stride, int bytes, int rows, int warp, int warps,
+                                              int lane) {
   const char* base = static_cast<const char*>(first);
-  const int lines = (bytes + 127) / 128 + 1;                  // (a run that starts inside a line touches one more)
-  for (int idx = tid; idx < rows * lines; idx += threads) {
-    const int row = idx / lines, at = (idx % lines) * 128;
-    if (at < bytes + 127) {
+  for (int row = warp; row < rows; row += warps)
+    for (int at = lane * 128; at < bytes + 127; at += 32 * 128) {       // (a run that starts inside a line touches one more)
       const char* ptr = base + (long long)row * stride + (at < bytes ? at : bytes - 1);
       asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
     }
-  }
 }
 
 // Thread (column quad lc, row group g) keeps rows [g R, (g + 1) R) of columns [4 lc, 4 lc + 4) of
@@ -178,58 +176,57 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
     // stage q, k (rotary and factor applied), the decays and v.  The loads are read-only ones
     // (what they read was finished before this kernel's wait returned), several in flight per
     // thread: a chunk's staging would otherwise cost as much as its arithmetic
+    // (a warp per token, lanes along the row: no division by a run-time length anywhere)
     auto where = [](int tok, int i) { return (tok * GROUPS + i / R) * RP + i % R; };
-#pragma unroll 4
-    for (int idx = tid; idx < n * half; idx += blockDim.x) {       // a pair (j, j + half) per turn
-      const int tok = idx / half, j = idx % half;
+    for (int tok = warp; tok < n; tok += warps) {
       const size_t t = base + tok;
-      const size_t at = (size_t)__ldg(p.positions + t) * half + j;
-      const float cs = __ldg(p.cos + at), sn = __ldg(p.sin + at);
-      const float ka = to_f32<T>(__ldg(k + t * p.ldk + j)), kb = to_f32<T>(__ldg(k + t * p.ldk + j + half));
-      sk[where(tok, j)] = (ka * cs - kb * sn) * p.k_scale;
-      sk[where(tok, j + half)] = (kb * cs + ka * sn) * p.k_scale;
-      if (MODE != SCAN_LOCAL) {
-        const float qa = to_f32<T>(__ldg(q + t * p.ldq + j)), qb = to_f32<T>(__ldg(q + t * p.ldq + j + half));
-        sq[where(tok, j)] = (qa * cs - qb * sn) * p.q_scale;
-        sq[where(tok, j + half)] = (qb * cs + qa * sn) * p.q_scale;
+      const T* kt = k + t * p.ldk;
+      const T* qt = q + t * p.ldq;
+      if (half > 0) {
+        const size_t at = (size_t)__ldg(p.positions + t) * half;
+#pragma unroll 2
+        for (int j = lane; j < half; j += 32) {                    // a pair (j, j + half) per turn
+          const float cs = __ldg(p.cos + at + j), sn = __ldg(p.sin + at + j);
+          const float ka = to_f32<T>(__ldg(kt + j)), kb = to_f32<T>(__ldg(kt + j + half));
+          sk[where(tok, j)] = (ka * cs - kb * sn) * p.k_scale;
+          sk[where(tok, j + half)] = (kb * cs + ka * sn) * p.k_scale;
+          if (MODE != SCAN_LOCAL) {
+            const float qa = to_f32<T>(__ldg(qt + j)), qb = to_f32<T>(__ldg(qt + j + half));
+            sq[where(tok, j)] = (qa * cs - qb * sn) * p.q_scale;
+            sq[where(tok, j + half)] = (qb * cs + qa * sn) * p.q_scale;
+          }
+        }
       }
-    }
-    const int plain = DIM - rot;
-#pragma unroll 4
-    for (int idx = tid; idx < n * plain; idx += blockDim.x) {      // the elements behind the rotary ones
-      const int tok = idx / plain, i = rot + idx % plain;
-      const size_t t = base + tok;
-      sk[where(tok, i)] = to_f32<T>(__ldg(k + t * p.ldk + i)) * p.k_scale;
-      if (MODE != SCAN_LOCAL) sq[where(tok, i)] = to_f32<T>(__ldg(q + t * p.ldq + i)) * p.q_scale;
-    }
-    if (PER_CHANNEL) {
-#pragma unroll 4
-      for (int idx = tid; idx < n * DIM; idx += blockDim.x) {
-        const int tok = idx / DIM, i = idx % DIM;
-        sa[where(tok, i)] = expf(log_sigmoid(__ldg(p.z + (size_t)(base + tok) * p.ldz + (size_t)h * DIM + i)) * p.inv_tau);
+#pragma unroll 2
+      for (int i = rot + lane; i < DIM; i += 32) {                 // the elements behind the rotary ones
+        sk[where(tok, i)] = to_f32<T>(__ldg(kt + i)) * p.k_scale;
+        if (MODE != SCAN_LOCAL) sq[where(tok, i)] = to_f32<T>(__ldg(qt + i)) * p.q_scale;
       }
-    }
+      if (PER_CHANNEL) {
+        const float* zt = p.z + t * p.ldz + (size_t)h * DIM;
+#pragma unroll 2
+        for (int i = lane; i < DIM; i += 32) sa[where(tok, i)] = expf(log_sigmoid(__ldg(zt + i)) * p.inv_tau);
+      }
+      const T* vt = v + t * p.ldv + col0;
 #pragma unroll 4
-    for (int idx = tid; idx < n * cols; idx += blockDim.x) {
-      const int tok = idx / cols, i = idx % cols;
-      sv[tok * cols + i] = col0 + i < vdim ? to_f32<T>(__ldg(v + (size_t)(base + tok) * p.ldv + col0 + i)) : 0.f;
+      for (int i = lane; i < cols; i += 32) sv[tok * cols + i] = col0 + i < vdim ? to_f32<T>(__ldg(vt + i)) : 0.f;
     }
     __syncthreads();
     if (turn + 1 < chunks) {        // the next chunk's operands, on their way while this one is computed
-      const int m = min(CHUNK, t1 - next), threads = blockDim.x;
+      const int m = min(CHUNK, t1 - next);
       const size_t t = next;
-      prefetch_rows(k + t * p.ldk, p.ldk * (long long)sizeof(T), DIM * (int)sizeof(T), m, tid, threads);
-      prefetch_rows(v + t * p.ldv + col0, p.ldv * (long long)sizeof(T), min(cols, vdim - col0) * (int)sizeof(T), m, tid, threads);
-      if (PER_CHANNEL) prefetch_rows(p.z + t * p.ldz + (size_t)h * DIM, p.ldz * 4, DIM * 4, m, tid, threads);
+      prefetch_rows(k + t * p.ldk, p.ldk * (long long)sizeof(T), DIM * (int)sizeof(T), m, warp, warps, lane);
+      prefetch_rows(v + t * p.ldv + col0, p.ldv * (long long)sizeof(T), min(cols, vdim - col0) * (int)sizeof(T), m, warp, warps, lane);
+      if (PER_CHANNEL) prefetch_rows(p.z + t * p.ldz + (size_t)h * DIM, p.ldz * 4, DIM * 4, m, warp, warps, lane);
       if (MODE != SCAN_LOCAL) {
-        prefetch_rows(q + t * p.ldq, p.ldq * (long long)sizeof(T), DIM * (int)sizeof(T), m, tid, threads);
+        prefetch_rows(q + t * p.ldq, p.ldq * (long long)sizeof(T), DIM * (int)sizeof(T), m, warp, warps, lane);
         if (p.gate && !p.raw_out)
-          prefetch_rows(gate + t * p.ldg, p.ldg * (long long)sizeof(T), vdim * (int)sizeof(T), m, tid, threads);
+          prefetch_rows(gate + t * p.ldg, p.ldg * (long long)sizeof(T), vdim * (int)sizeof(T), m, warp, warps, lane);
       }
       if (half > 0) {
         const size_t at = (size_t)__ldg(p.positions + t) * half;          // (a request's positions in a step are consecutive)
-        prefetch_rows(p.cos + at, half * 4, half * 4, m, tid, threads);
-        prefetch_rows(p.sin + at, half * 4, half * 4, m, tid, threads);
+        prefetch_rows(p.cos + at, half * 4, half * 4, m, warp, warps, lane);
+        prefetch_rows(p.sin + at, half * 4, half * 4, m, warp, warps, lane);
       }
     }
     if (in_block) {       // (whole warps or none: cols is a multiple of 32 / GROUPS columns quads, see the launch)
@@ -432,6 +429,13 @@ static int block_columns(int vdim) {
 
 // blocks that a head of `vdim` value columns is spread over (more than one: the caller brings a
 // 32-bit scratch [T, H * vdim] for the outputs before their norm)
+// blocks of the scan that an SM holds at once for heads of `vdim` value columns (128 registers a thread)
+TS_EXPORT int ts_linear_attention_resident_blocks(int vdim) {
+  const int threads = block_columns(vdim) / COLS * GROUPS;
+  const int fit = MAX_THREADS / threads;
+  return fit < 1 ? 1 : (fit > 8 ? 8 : fit);
+}
+
 TS_EXPORT int ts_linear_attention_column_tiles(int vdim) {
   const int cols = block_columns(vdim);
   return (vdim + cols - 1) / cols;

@@ -1229,17 +1229,18 @@ LINEAR_ATTENTION_MAX_VALUE_DIM = 4096
 #: a step whose longest portion has at least LINEAR_ATTENTION_SEGMENT_MIN tokens cuts its portions
 #: into segments that run side by side (three launches instead of one: local states, their
 #: combination, outputs); the segments are as long as lets the longest portion's blocks fill the
-#: SMs once (two blocks per SM), a multiple of 16 tokens and at least LINEAR_ATTENTION_SEGMENT
+#: SMs once (as many blocks per SM as fit), a multiple of 16 tokens and at least LINEAR_ATTENTION_SEGMENT
 LINEAR_ATTENTION_SEGMENT = 64
 LINEAR_ATTENTION_SEGMENT_MIN = 256
 
 
-def linear_attention_segment(longest: int, blocks_per_segment: int) -> int:
+def linear_attention_segment(longest: int, blocks_per_segment: int, resident: int = 2) -> int:
     """Tokens per segment for a step whose longest portion has ``longest`` tokens and launches
-    ``blocks_per_segment`` blocks (heads x column tiles) per segment; 0: one segment, one launch."""
+    ``blocks_per_segment`` blocks (heads x column tiles) per segment, ``resident`` of which an SM
+    holds at once; 0: one segment, one launch."""
     if longest < LINEAR_ATTENTION_SEGMENT_MIN:
         return 0
-    segments = max(1, 2 * num_sms() // max(1, blocks_per_segment))
+    segments = max(1, resident * num_sms() // max(1, blocks_per_segment))
     length = max(LINEAR_ATTENTION_SEGMENT, -(-longest // segments))
     return -(-length // 16) * 16
 
@@ -1287,7 +1288,8 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
     tiles = lib.ts_linear_attention_column_tiles(c_int(value_dim))
     wide = tiles > 1
     if segment is None:
-        seg_len = linear_attention_segment(getattr(ctx, "max_q_len", 0), H * tiles)
+        seg_len = linear_attention_segment(getattr(ctx, "max_q_len", 0), H * tiles,
+                                           lib.ts_linear_attention_resident_blocks(c_int(value_dim)))
     else:
         seg_len = int(segment)
     max_segments, seg_state, seg_decay = 0, None, None
