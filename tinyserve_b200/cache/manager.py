@@ -59,6 +59,7 @@ class PagePool:
 class GroupSpec:
     kind: str                    # "full" or "window"
     window: int = 0
+    keep_first: int = 0          # "window": the first tokens of a sequence stay visible, their pages are never released
 
 
 @dataclass
@@ -175,7 +176,8 @@ class CacheManager:
 
     def _release_behind(self, rid, g, rp, num_computed) -> None:
         first = min(self._first_needed_page(g, num_computed), len(rp.pages))
-        for logical in range(rp.first_live, first):
+        kept_pages = -(-self.groups[g].keep_first // self.page_size)      # pages that hold kept first tokens
+        for logical in range(max(rp.first_live, kept_pages), first):
             page = rp.pages[logical]
             if page:
                 self.pools[g].give_back(page, rid)

@@ -11,6 +11,7 @@ from __future__ import annotations
 import json
 import os
 
+from .delilorn import DelilornConfig
 from .dudatar import DudatarConfig
 from .model_config import ConfigError, ModelConfig, Qwen3Config
 
@@ -60,3 +61,4 @@ def load_model_config(model_dir: str) -> ModelConfig:
 
 register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(DudatarConfig.architecture, DudatarConfig)
+register_architecture(DelilornConfig.architecture, DelilornConfig)

@@ -5,7 +5,9 @@
 //
 // Behaviour follows serve.py:639-688: request b's queries are rows cu_q[b]..cu_q[b+1] of
 // q; query i stands at position kv_len - q_len + i; key j is visible iff j <= position
-// (and, with a window W > 0, j > position - W); query head h reads KV head h / (H / Hkv);
+// (and, with a window W > 0, j > position - W or j < keep_first: the first keys of a sequence
+// may stay visible to every query behind them); query head h reads KV head h / (H / Hkv);
+// with `sinks`, head h's softmax sum also holds exp(sinks[h]), a term without key or value;
 // keys are found through the request's block table.  Online softmax as
 // tinykernels.py:386-413, but with every product and sum in 32-bit.
 //
@@ -44,6 +46,8 @@ struct AttnParams {
   int H, Hkv, page_size, max_blocks;
   int heads_per_tile, queries_per_tile, head_tiles;
   int num_splits, window;
+  int keep_first;           // with a window: keys below this stay visible
+  const float* sinks;       // [H] or null: one more term exp(sinks[h]) in every softmax sum of head h
   float scale;
 };
 
@@ -109,10 +113,13 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
   const int j_hi = min(kv_len, pos0 + nq);
   const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int first_tile = j_lo / BN;
-  const int total_tiles = (j_hi + BN - 1) / BN - first_tile;
+  // the tiles of the kept first keys that lie before the window's first tile come first in the walk
+  const int keep = p.window > 0 ? min(p.keep_first, j_hi) : 0;
+  const int kept_tiles = min((keep + BN - 1) / BN, first_tile);
+  const int total_tiles = (j_hi + BN - 1) / BN - first_tile + kept_tiles;
   const int per_split = (total_tiles + p.num_splits - 1) / p.num_splits;
-  const int tile_begin = first_tile + split * per_split;
-  const int tile_end = min(first_tile + total_tiles, tile_begin + per_split);
+  const int tile_begin = split * per_split;
+  const int tile_end = min(total_tiles, tile_begin + per_split);
 
   float m[RPW], l[RPW], acc[RPW][DC];
 #pragma unroll
@@ -125,14 +132,15 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
 
   constexpr int VN = Vec16<T>::N, CHUNKS = D / VN;
   const int* bt = p.block_table + (size_t)b * p.max_blocks;
-  for (int tile = tile_begin; tile < tile_end; ++tile) {
+  for (int walk = tile_begin; walk < tile_end; ++walk) {
+    const int tile = walk < kept_tiles ? walk : first_tile + (walk - kept_tiles);
     const int j0 = tile * BN;
     __syncthreads();   // the previous tile's keys and values are no longer read
     for (int i = threadIdx.x; i < BN * CHUNKS; i += WARPS * 32) {
       const int key = i / CHUNKS, c = (i % CHUNKS) * VN;
       const int j = j0 + key;
       float kv[VN], vv[VN];
-      if (j >= j_lo && j < j_hi) {
+      if ((j >= j_lo || j < keep) && j < j_hi) {
         const size_t page = bt[j / p.page_size];
         const size_t off = ((page * p.Hkv + kvh) * p.page_size + j % p.page_size) * D + c;
         load_row_chunk<T>(kc + off, kv);
@@ -162,7 +170,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
       for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
       s *= p.scale;
       const int pos = pos0 + (p.queries_per_tile > 1 ? r / GT : 0);
-      const bool visible = j <= pos && j < j_hi && (p.window <= 0 || j > pos - p.window);
+      const bool visible = j <= pos && j < j_hi && (p.window <= 0 || j > pos - p.window || j < keep);
       s = visible ? s : -INFINITY;
       const float m_new = fmaxf(m[i], warp_max(s));
       const float prob = (s == -INFINITY) ? 0.f : expf(s - m_new);
@@ -199,6 +207,14 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
     const int qi = p.queries_per_tile > 1 ? r / GT : 0, g = r % GT;
     const size_t row = (size_t)(q_begin + q0 + qi) * p.H + kvh * G + g0 + g;
     if (p.num_splits == 1) {
+      if (p.sinks) {
+        const float sink = p.sinks[kvh * G + g0 + g];
+        const float m_new = fmaxf(m[i], sink);
+        const float alpha = (m[i] == -INFINITY) ? 0.f : expf(m[i] - m_new);
+        l[i] = l[i] * alpha + expf(sink - m_new);
+#pragma unroll
+        for (int c = 0; c < DC; ++c) acc[i][c] *= alpha;
+      }
       const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
       T* o = static_cast<T*>(p.out) + row * D;
 #pragma unroll
@@ -221,14 +237,16 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, T* __restrict__ out,
-                                         int num_splits) {
+                                         int num_splits, const float* __restrict__ sinks, int H) {
   pdl_trigger();
   pdl_wait();
   const size_t row = blockIdx.x;
   const float* ml = part_ml + row * num_splits * 2;
   float m = -INFINITY;
   for (int s = 0; s < num_splits; ++s) m = fmaxf(m, ml[2 * s]);
-  float denom = 0.f;
+  const float sink = sinks ? sinks[row % H] : -INFINITY;
+  m = fmaxf(m, sink);
+  float denom = sinks ? expf(sink - m) : 0.f;
   for (int s = 0; s < num_splits; ++s)
     denom += (ml[2 * s] == -INFINITY) ? 0.f : expf(ml[2 * s] - m) * ml[2 * s + 1];
   const float inv = denom > 0.f ? 1.f / denom : 0.f;
@@ -254,8 +272,9 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
                                  const int* kv_lens, int num_tokens, int num_requests,
                                  int max_q_len, int H, int Hkv, int page_size, int max_blocks,
                                  float scale, int window, int num_splits, float* part_o,
-                                 float* part_ml, cudaStream_t stream) {
+                                 float* part_ml, int keep_first, const float* sinks, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention: empty batch");
+  TS_REQUIRE(keep_first >= 0, "paged_attention: keep_first %d", keep_first);
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && max_blocks > 0, "paged_attention: bad page geometry");
   TS_REQUIRE(num_splits >= 1 && num_splits <= 64, "paged_attention: num_splits %d out of range", num_splits);
@@ -271,6 +290,7 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
   p.queries_per_tile = G < BM ? BM / G : 1;
   p.head_tiles = (G + p.heads_per_tile - 1) / p.heads_per_tile;
   p.num_splits = num_splits; p.window = window; p.scale = scale;
+  p.keep_first = keep_first; p.sinks = sinks;
   const long long gz = (long long)num_requests * num_splits;
   const long long gy = (long long)Hkv * p.head_tiles;
   TS_REQUIRE(gz <= 65535 && gy <= 65535, "paged_attention: grid too large (%lld requests*splits, %lld head tiles)", gz, gy);
@@ -289,9 +309,9 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
   if (num_splits > 1) {
     const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);
     if (dtype == TS_F32)
-      TS_LAUNCH("attention_combine", attention_combine_kernel<float>, num_tokens * H, threads, 0, stream, (const float*)part_o, (const float*)part_ml, (float*)out, num_splits);
+      TS_LAUNCH("attention_combine", attention_combine_kernel<float>, num_tokens * H, threads, 0, stream, (const float*)part_o, (const float*)part_ml, (float*)out, num_splits, sinks, H);
     else
-      TS_LAUNCH("attention_combine", attention_combine_kernel<__nv_bfloat16>, num_tokens * H, threads, 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, num_splits);
+      TS_LAUNCH("attention_combine", attention_combine_kernel<__nv_bfloat16>, num_tokens * H, threads, 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, num_splits, sinks, H);
   }
   return 0;
 }
@@ -345,5 +365,5 @@ TS_EXPORT int ts_paged_attention_static_scratch(
   float* part_ml = part_o + rows * D;
   return ts_paged_attention(dtype, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                             num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window,
-                            num_splits, part_o, part_ml, stream);
+                            num_splits, part_o, part_ml, 0, nullptr, stream);
 }

@@ -1,0 +1,351 @@
+// Kernels around latent attention, around a mixture of experts, and the norm of a block that
+// norms its sub-layers' outputs as well as their inputs.  Everything here is 32-bit arithmetic
+// on rows; inputs and outputs are float or bfloat16.
+//
+//  * ts_normed_add_rmsnorm: residual += y / rms(y) * w_post; out = residual / rms(residual) * w_pre
+//    (the second norm of one sub-layer and the first of the next in one pass over the row).
+//  * ts_latent_prepare: from one fused projection of a token, the query latent (RMS-normed) and
+//    what the cache keeps of the token: the RMS-normed key/value latent followed by the one
+//    rotated key part that all heads share, written to the token's cache slot.
+//  * ts_latent_query: the query rows the attention kernel reads: per head the query carried into
+//    the latent space followed by its rotated part, padded with zeros to the stored width.
+//  * ts_gate_heads: out[t, h, :] = x[h, t, :] * sigmoid(gate[t, h, :]).
+//  * ts_moe_route: softmax over all experts of a token's router logits; the `top` largest keep
+//    their probability (not renormalised), the others get zero.
+//  * ts_moe_activate: a[t, e, :] <- act(a[t, e, :]) * gate[t, e], act = relu squared.
+//  * ts_batched_matmul: C[b] = A[b] B[b] with 32-bit FMA (any strides), chains of 64 k.
+#include "common.cuh"
+
+TS_DEFINE_LAST_ERROR()
+
+namespace {
+
+// ------------------------------------------------------------------ post-norm, add, pre-norm
+template <typename T>
+__global__ void normed_add_rmsnorm_kernel(const T* __restrict__ y, VecParam w_post, float* __restrict__ residual,
+                                          VecParam w_pre, float eps_post, float eps_pre, T* __restrict__ out,
+                                          const int* __restrict__ rows, int n, int write_residual) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t m = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* r = residual + m * n;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float v = to_f32<T>(y[m * n + c]);
+    row[c] = v;
+    sq += v * v;
+  }
+  const float rstd_y = rsqrtf(block_sum(sq, scratch) / (float)n + eps_post);
+  sq = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float v = r[c] + row[c] * rstd_y * w_post[c];
+    if (write_residual) r[c] = v;
+    row[c] = v;
+    sq += v * v;
+  }
+  if (out == nullptr) return;
+  const float rstd = rsqrtf(block_sum(sq, scratch) / (float)n + eps_pre);
+  T* o = out + (size_t)blockIdx.x * n;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) o[c] = from_f32<T>(row[c] * rstd * w_pre[c]);
+}
+
+// ------------------------------------------------------------------ latent attention: what a token leaves
+struct LatentPrepare {
+  const void* proj; long long ld;         // [T, >= q_rank + kv_rank + rot_dim]: query latent | kv latent | shared key part
+  int q_rank, kv_rank, rot_dim, stored;   // stored: width of a cache row, >= kv_rank + rot_dim
+  int has_kv;                             // 0: the projection holds the query latent only
+  VecParam q_weight, kv_weight;
+  float eps;
+  const int* positions; const float* cos; const float* sin;   // tables [positions, rot_dim / 2]
+  void* q_latent;                         // [T, q_rank]
+  void* cache; const int* slot_mapping;   // [slots, stored]; slot < 0: nothing is written
+};
+
+template <typename T>
+__global__ void latent_prepare_kernel(LatentPrepare p) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  const T* x = static_cast<const T*>(p.proj) + t * p.ld;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < p.q_rank; c += blockDim.x) {
+    const float v = to_f32<T>(x[c]);
+    sq += v * v;
+  }
+  const float rq = rsqrtf(block_sum(sq, scratch) / (float)p.q_rank + p.eps);
+  T* ql = static_cast<T*>(p.q_latent) + t * p.q_rank;
+  for (int c = threadIdx.x; c < p.q_rank; c += blockDim.x) ql[c] = from_f32<T>(to_f32<T>(x[c]) * rq * p.q_weight[c]);
+  if (!p.has_kv) return;
+  const int slot = p.slot_mapping ? p.slot_mapping[t] : -1;
+  if (slot < 0) return;
+  const T* kv = x + p.q_rank;
+  sq = 0.f;
+  for (int c = threadIdx.x; c < p.kv_rank; c += blockDim.x) {
+    const float v = to_f32<T>(kv[c]);
+    sq += v * v;
+  }
+  const float rk = rsqrtf(block_sum(sq, scratch) / (float)p.kv_rank + p.eps);
+  T* dst = static_cast<T*>(p.cache) + (size_t)slot * p.stored;
+  for (int c = threadIdx.x; c < p.kv_rank; c += blockDim.x) dst[c] = from_f32<T>(to_f32<T>(kv[c]) * rk * p.kv_weight[c]);
+  const int half = p.rot_dim >> 1;
+  const size_t at = (size_t)p.positions[t] * half;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    const float a = to_f32<T>(kv[p.kv_rank + j]), b = to_f32<T>(kv[p.kv_rank + j + half]);
+    const float cs = p.cos[at + j], sn = p.sin[at + j];
+    dst[p.kv_rank + j] = from_f32<T>(a * cs - b * sn);
+    dst[p.kv_rank + j + half] = from_f32<T>(b * cs + a * sn);
+  }
+  for (int c = p.kv_rank + p.rot_dim + threadIdx.x; c < p.stored; c += blockDim.x) dst[c] = from_f32<T>(0.f);
+}
+
+// ------------------------------------------------------------------ latent attention: query rows
+// out[t, h, :] = [ carried[h, t, :kv_rank] | rotate(q[t, h, dim : dim + rot_dim]) | 0 ]
+template <typename T>
+__global__ void latent_query_kernel(const T* __restrict__ carried, const T* __restrict__ q, long long ldq, int H, int dim,
+                                    int rot_dim, int kv_rank, int stored, const int* __restrict__ positions,
+                                    const float* __restrict__ cos, const float* __restrict__ sin, T* __restrict__ out,
+                                    int num_tokens) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  const int half = rot_dim >> 1;
+  const size_t at = (size_t)positions[t] * half;
+  for (int h = blockIdx.y; h < H; h += gridDim.y) {
+    const T* src = carried + ((size_t)h * num_tokens + t) * kv_rank;
+    T* dst = out + (t * H + h) * stored;
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) dst[c] = src[c];
+    const T* qr = q + t * ldq + (size_t)h * (dim + rot_dim) + dim;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      const float a = to_f32<T>(qr[j]), b = to_f32<T>(qr[j + half]);
+      const float cs = cos[at + j], sn = sin[at + j];
+      dst[kv_rank + j] = from_f32<T>(a * cs - b * sn);
+      dst[kv_rank + j + half] = from_f32<T>(b * cs + a * sn);
+    }
+    for (int c = kv_rank + rot_dim + threadIdx.x; c < stored; c += blockDim.x) dst[c] = from_f32<T>(0.f);
+  }
+}
+
+// out[t, h * n + c] = x[h, t, c] * sigmoid(gate[t * ldg + h * n + c])
+template <typename T>
+__global__ void gate_heads_kernel(const T* __restrict__ x, const T* __restrict__ gate, long long ldg, T* __restrict__ out,
+                                  int H, int n, int num_tokens) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < H * n; i += blockDim.x) {
+    const int h = i / n, c = i % n;
+    const float g = to_f32<T>(gate[t * ldg + i]);
+    out[t * H * n + i] = from_f32<T>(to_f32<T>(x[((size_t)h * num_tokens + t) * n + c]) / (1.f + expf(-g)));
+  }
+}
+
+// ------------------------------------------------------------------ mixture of experts
+// a warp per token: probabilities of all experts, the `top` largest kept (ties: the lower number)
+__global__ void moe_route_kernel(const float* __restrict__ logits, float* __restrict__ gates, int num_tokens, int E, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= num_tokens) return;
+  const float* z = logits + (size_t)t * E;
+  float* g = gates + (size_t)t * E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int e = lane; e < E; e += 32) g[e] = -expf(z[e] - mx) * inv;      // negative: not chosen yet
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = 0.f;                 // the largest probability among those not chosen yet
+    int best_e = E;
+    for (int e = lane; e < E; e += 32) {
+      const float v = -g[e];
+      if (v > best || (v == best && v > 0.f && e < best_e)) { best = v; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if (lane == 0 && best_e < E) g[best_e] = best;
+    __syncwarp();
+  }
+  for (int e = lane; e < E; e += 32)
+    if (g[e] < 0.f) g[e] = 0.f;
+}
+
+// a[t, e * ff + j] <- relu(a)^2 * gates[t, e]
+template <typename T>
+__global__ void moe_activate_kernel(T* __restrict__ a, const float* __restrict__ gates, int E, int ff) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  T* row = a + t * (size_t)E * ff;
+  for (int i = threadIdx.x; i < E * ff; i += blockDim.x) {
+    const float g = gates[t * E + i / ff];
+    const float v = fmaxf(to_f32<T>(row[i]), 0.f);
+    row[i] = from_f32<T>(g == 0.f ? 0.f : v * v * g);
+  }
+}
+
+// ------------------------------------------------------------------ batched 32-bit product
+// C[b, m, n] = sum_k A[b, m, k] B[b, k, n]; 32 x 32 tiles, a thread makes a 2 x 2 corner, k in
+// chains of 64 whose results are added in order (as the package's FMA product does)
+constexpr int BT = 32, BKK = 16;
+template <typename T>
+__global__ void __launch_bounds__(256) batched_matmul_kernel(const T* __restrict__ A, long long sab, long long sam, long long sak,
+                                                             const T* __restrict__ B, long long sbb, long long sbk, long long sbn,
+                                                             T* __restrict__ C, int M, int N, int K) {
+  __shared__ float As[BKK][BT + 1];
+  __shared__ float Bs[BKK][BT + 1];
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.z, m0 = blockIdx.y * BT, n0 = blockIdx.x * BT;
+  const T* a = A + (size_t)b * sab;
+  const T* w = B + (size_t)b * sbb;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, part[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  for (int k0 = 0; k0 < K; k0 += BKK) {
+    for (int i = threadIdx.x; i < BT * BKK; i += 256) {
+      const int r = i / BKK, k = i % BKK;
+      As[k][r] = (m0 + r < M && k0 + k < K) ? to_f32<T>(a[(size_t)(m0 + r) * sam + (size_t)(k0 + k) * sak]) : 0.f;
+      const int kk = i / BT, c = i % BT;
+      Bs[kk][c] = (n0 + c < N && k0 + kk < K) ? to_f32<T>(w[(size_t)(k0 + kk) * sbk + (size_t)(n0 + c) * sbn]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BKK; ++k) {
+      const float a0 = As[k][ty], a1 = As[k][ty + 16], b0 = Bs[k][tx], b1 = Bs[k][tx + 16];
+      part[0][0] = fmaf(a0, b0, part[0][0]); part[0][1] = fmaf(a0, b1, part[0][1]);
+      part[1][0] = fmaf(a1, b0, part[1][0]); part[1][1] = fmaf(a1, b1, part[1][1]);
+    }
+    if ((k0 + BKK) % 64 == 0 || k0 + BKK >= K) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) { acc[i][j] += part[i][j]; part[i][j] = 0.f; }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int m = m0 + ty + 16 * i, n = n0 + tx + 16 * j;
+      if (m < M && n < N) C[((size_t)b * M + m) * N + n] = from_f32<T>(acc[i][j]);
+    }
+}
+
+}  // namespace
+
+TS_EXPORT int ts_normed_add_rmsnorm(int dtype, const void* y, const void* w_post, int w_post_is_f32, float* residual,
+                                    const void* w_pre, int w_pre_is_f32, float eps_post, float eps_pre, void* out,
+                                    const int* rows, int num_out_rows, int n, int write_residual, cudaStream_t stream) {
+  TS_REQUIRE(num_out_rows > 0 && n > 0 && y && residual && w_post, "normed_add_rmsnorm: empty input");
+  TS_REQUIRE(out == nullptr || w_pre != nullptr, "normed_add_rmsnorm: an output without a weight");
+  const size_t smem = (size_t)n * sizeof(float);
+  TS_REQUIRE(smem <= 200 * 1024, "normed_add_rmsnorm: rows of %d elements are too long", n);
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  VecParam wa{w_post, w_post_is_f32}, wb{w_pre, w_pre_is_f32};
+  if (dtype == TS_F32) {
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(normed_add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return ts_fail("normed_add_rmsnorm: shared memory");
+    TS_LAUNCH("normed_add_rmsnorm", normed_add_rmsnorm_kernel<float>, num_out_rows, threads, smem, stream, (const float*)y, wa,
+              residual, wb, eps_post, eps_pre, (float*)out, rows, n, write_residual);
+  } else if (dtype == TS_BF16) {
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(normed_add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return ts_fail("normed_add_rmsnorm: shared memory");
+    TS_LAUNCH("normed_add_rmsnorm", normed_add_rmsnorm_kernel<__nv_bfloat16>, num_out_rows, threads, smem, stream,
+              (const __nv_bfloat16*)y, wa, residual, wb, eps_post, eps_pre, (__nv_bfloat16*)out, rows, n, write_residual);
+  } else {
+    return ts_fail("normed_add_rmsnorm: unknown dtype %d", dtype);
+  }
+  return 0;
+}
+
+TS_EXPORT int ts_latent_prepare(int dtype, const void* proj, long long ld, int q_rank, int kv_rank, int rot_dim, int stored,
+                                int has_kv, const void* q_weight, int q_weight_is_f32, const void* kv_weight,
+                                int kv_weight_is_f32, float eps, const int* positions, const float* cos, const float* sin,
+                                void* q_latent, void* cache, const int* slot_mapping, int num_tokens, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && q_rank > 0 && proj && q_weight && q_latent, "latent_prepare: empty input");
+  TS_REQUIRE(!has_kv || (kv_rank > 0 && rot_dim >= 0 && rot_dim % 2 == 0 && stored >= kv_rank + rot_dim && kv_weight),
+             "latent_prepare: a latent of %d with a rotated part of %d does not fit rows of %d", kv_rank, rot_dim, stored);
+  TS_REQUIRE(!has_kv || rot_dim == 0 || (positions && cos && sin), "latent_prepare: rotation without tables");
+  LatentPrepare p{proj, ld, q_rank, kv_rank, rot_dim, stored, has_kv, VecParam{q_weight, q_weight_is_f32},
+                  VecParam{kv_weight, kv_weight_is_f32}, eps, positions, cos, sin, q_latent, cache,
+                  cache ? slot_mapping : nullptr};
+  const int widest = q_rank > kv_rank ? q_rank : kv_rank;
+  const int threads = widest >= 1024 ? 256 : 128;
+  if (dtype == TS_F32) TS_LAUNCH("latent_prepare", latent_prepare_kernel<float>, num_tokens, threads, 0, stream, p);
+  else if (dtype == TS_BF16) TS_LAUNCH("latent_prepare", latent_prepare_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, p);
+  else return ts_fail("latent_prepare: unknown dtype %d", dtype);
+  return 0;
+}
+
+TS_EXPORT int ts_latent_query(int dtype, const void* carried, const void* q, long long ldq, int H, int dim, int rot_dim,
+                              int kv_rank, int stored, const int* positions, const float* cos, const float* sin, void* out,
+                              int num_tokens, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && H > 0 && kv_rank > 0 && stored >= kv_rank + rot_dim && rot_dim % 2 == 0 && carried && q && out,
+             "latent_query: sizes do not fit");
+  TS_REQUIRE(rot_dim == 0 || (positions && cos && sin), "latent_query: rotation without tables");
+  dim3 grid(num_tokens, H < 16 ? H : 16);
+  if (dtype == TS_F32)
+    TS_LAUNCH("latent_query", latent_query_kernel<float>, grid, 128, 0, stream, (const float*)carried, (const float*)q, ldq, H, dim,
+              rot_dim, kv_rank, stored, positions, cos, sin, (float*)out, num_tokens);
+  else if (dtype == TS_BF16)
+    TS_LAUNCH("latent_query", latent_query_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)carried,
+              (const __nv_bfloat16*)q, ldq, H, dim, rot_dim, kv_rank, stored, positions, cos, sin, (__nv_bfloat16*)out, num_tokens);
+  else return ts_fail("latent_query: unknown dtype %d", dtype);
+  return 0;
+}
+
+TS_EXPORT int ts_gate_heads(int dtype, const void* x, const void* gate, long long ldg, void* out, int H, int n, int num_tokens,
+                            cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && H > 0 && n > 0 && x && gate && out, "gate_heads: empty input");
+  const int threads = H * n >= 1024 ? 256 : 128;
+  if (dtype == TS_F32)
+    TS_LAUNCH("gate_heads", gate_heads_kernel<float>, num_tokens, threads, 0, stream, (const float*)x, (const float*)gate, ldg,
+              (float*)out, H, n, num_tokens);
+  else if (dtype == TS_BF16)
+    TS_LAUNCH("gate_heads", gate_heads_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)x,
+              (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, H, n, num_tokens);
+  else return ts_fail("gate_heads: unknown dtype %d", dtype);
+  return 0;
+}
+
+TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, int E, int top, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && E > 0 && top > 0 && top <= E && logits && gates, "moe_route: %d of %d experts", top, E);
+  TS_LAUNCH("moe_route", moe_route_kernel, (num_tokens + 3) / 4, 128, 0, stream, logits, gates, num_tokens, E, top);
+  return 0;
+}
+
+TS_EXPORT int ts_moe_activate(int dtype, void* a, const float* gates, int num_tokens, int E, int ff, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && E > 0 && ff > 0 && a && gates, "moe_activate: empty input");
+  if (dtype == TS_F32) TS_LAUNCH("moe_activate", moe_activate_kernel<float>, num_tokens, 256, 0, stream, (float*)a, gates, E, ff);
+  else if (dtype == TS_BF16) TS_LAUNCH("moe_activate", moe_activate_kernel<__nv_bfloat16>, num_tokens, 256, 0, stream, (__nv_bfloat16*)a, gates, E, ff);
+  else return ts_fail("moe_activate: unknown dtype %d", dtype);
+  return 0;
+}
+
+TS_EXPORT int ts_batched_matmul(int dtype, const void* A, long long sab, long long sam, long long sak, const void* B,
+                                long long sbb, long long sbk, long long sbn, void* C, int batch, int M, int N, int K,
+                                cudaStream_t stream) {
+  TS_REQUIRE(batch > 0 && M > 0 && N > 0 && K > 0 && A && B && C, "batched_matmul: empty operand");
+  dim3 grid((N + BT - 1) / BT, (M + BT - 1) / BT, batch);
+  TS_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "batched_matmul: grid too large");
+  if (dtype == TS_F32)
+    TS_LAUNCH("batched_matmul", batched_matmul_kernel<float>, grid, 256, 0, stream, (const float*)A, sab, sam, sak, (const float*)B,
+              sbb, sbk, sbn, (float*)C, M, N, K);
+  else if (dtype == TS_BF16)
+    TS_LAUNCH("batched_matmul", batched_matmul_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)A, sab, sam, sak,
+              (const __nv_bfloat16*)B, sbb, sbk, sbn, (__nv_bfloat16*)C, M, N, K);
+  else return ts_fail("batched_matmul: unknown dtype %d", dtype);
+  return 0;
+}

@@ -83,8 +83,17 @@ struct ScanParams {
   float* seg_decay;                       // [B, H, segments, DIM]: product of a segment's decays (per channel)
   int max_segments;
   int cols, col_tiles;                    // value columns per block (a multiple of COLS); blocks per head
-  float* raw_out;                         // [T, H * vdim] 32-bit o_t before norm and gate (col_tiles > 1), else null
+  float* raw_out;                         // [T, H * vdim] 32-bit o_t before norm and gate (col_tiles > 1 or joint_norm), else null
+  int in_act;                             // 1: q, k and v pass through silu as they are staged
+  int gate_act;                           // 0: the output is multiplied by silu(gate), 1: by sigmoid(gate)
+  int joint_norm;                         // 1: the output norm runs over all heads of a token together (weight [H * vdim])
 };
+
+__device__ __forceinline__ float staged(float x, int in_act) { return in_act ? x / (1.f + expf(-x)) : x; }
+__device__ __forceinline__ float gate_factor(float g, int gate_act) {
+  const float s = 1.f / (1.f + expf(-g));
+  return gate_act ? s : g * s;
+}
 
 enum { SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FROM_SEGMENT = 2 };
 
@@ -187,11 +196,11 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
 #pragma unroll 2
         for (int j = lane; j < half; j += 32) {                    // a pair (j, j + half) per turn
           const float cs = __ldg(p.cos + at + j), sn = __ldg(p.sin + at + j);
-          const float ka = to_f32<T>(__ldg(kt + j)), kb = to_f32<T>(__ldg(kt + j + half));
+          const float ka = staged(to_f32<T>(__ldg(kt + j)), p.in_act), kb = staged(to_f32<T>(__ldg(kt + j + half)), p.in_act);
           sk[where(tok, j)] = (ka * cs - kb * sn) * p.k_scale;
           sk[where(tok, j + half)] = (kb * cs + ka * sn) * p.k_scale;
           if (MODE != SCAN_LOCAL) {
-            const float qa = to_f32<T>(__ldg(qt + j)), qb = to_f32<T>(__ldg(qt + j + half));
+            const float qa = staged(to_f32<T>(__ldg(qt + j)), p.in_act), qb = staged(to_f32<T>(__ldg(qt + j + half)), p.in_act);
             sq[where(tok, j)] = (qa * cs - qb * sn) * p.q_scale;
             sq[where(tok, j + half)] = (qb * cs + qa * sn) * p.q_scale;
           }
@@ -199,8 +208,8 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       }
 #pragma unroll 2
       for (int i = rot + lane; i < DIM; i += 32) {                 // the elements behind the rotary ones
-        sk[where(tok, i)] = to_f32<T>(__ldg(kt + i)) * p.k_scale;
-        if (MODE != SCAN_LOCAL) sq[where(tok, i)] = to_f32<T>(__ldg(qt + i)) * p.q_scale;
+        sk[where(tok, i)] = staged(to_f32<T>(__ldg(kt + i)), p.in_act) * p.k_scale;
+        if (MODE != SCAN_LOCAL) sq[where(tok, i)] = staged(to_f32<T>(__ldg(qt + i)), p.in_act) * p.q_scale;
       }
       if (PER_CHANNEL) {
         const float* zt = p.z + t * p.ldz + (size_t)h * DIM;
@@ -209,7 +218,7 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       }
       const T* vt = v + t * p.ldv + col0;
 #pragma unroll 4
-      for (int i = lane; i < cols; i += 32) sv[tok * cols + i] = col0 + i < vdim ? to_f32<T>(__ldg(vt + i)) : 0.f;
+      for (int i = lane; i < cols; i += 32) sv[tok * cols + i] = col0 + i < vdim ? staged(to_f32<T>(__ldg(vt + i)), p.in_act) : 0.f;
     }
     __syncthreads();
     if (turn + 1 < chunks) {        // the next chunk's operands, on their way while this one is computed
@@ -288,8 +297,7 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
         float o = so[tok * cols + i] * rstd;
         if (p.norm_weight) o *= nw[i];
         if (p.gate) {
-          const float gv = to_f32<T>(gate[t * p.ldg + i]);
-          o *= gv / (1.f + expf(-gv));
+          o *= gate_factor(to_f32<T>(gate[t * p.ldg + i]), p.gate_act);
         }
         out[t * p.ldo + i] = from_f32<T>(o);
       }
@@ -325,6 +333,21 @@ __global__ void linear_attention_finish_kernel(ScanParams p, int num_tokens) {
   const size_t t = blockIdx.x;
   const int vdim = p.vdim;
   VecParam nw{p.norm_weight, p.norm_weight_is_f32};
+  if (p.joint_norm) {           // one norm over all heads of the token
+    __shared__ float scratch[33];
+    const int n = p.H * vdim;
+    const float* o = p.raw_out + t * n;
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) acc += o[i] * o[i];
+    const float rstd = rsqrtf(block_sum(acc, scratch) / (float)n + p.eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float y = o[i] * rstd;
+      if (p.norm_weight) y *= nw[i];
+      if (p.gate) y *= gate_factor(to_f32<T>(static_cast<const T*>(p.gate)[t * p.ldg + i]), p.gate_act);
+      static_cast<T*>(p.out)[t * p.ldo + i] = from_f32<T>(y);
+    }
+    return;
+  }
   for (int h = warp; h < p.H; h += warps) {
     const float* o = p.raw_out + t * p.H * vdim + (size_t)h * vdim;
     float acc = 0.f;
@@ -334,8 +357,7 @@ __global__ void linear_attention_finish_kernel(ScanParams p, int num_tokens) {
       float y = o[i] * rstd;
       if (p.norm_weight) y *= nw[i];
       if (p.gate) {
-        const float gv = to_f32<T>(static_cast<const T*>(p.gate)[t * p.ldg + (size_t)h * vdim + i]);
-        y *= gv / (1.f + expf(-gv));
+        y *= gate_factor(to_f32<T>(static_cast<const T*>(p.gate)[t * p.ldg + (size_t)h * vdim + i]), p.gate_act);
       }
       static_cast<T*>(p.out)[t * p.ldo + (size_t)h * vdim + i] = from_f32<T>(y);
     }
@@ -448,13 +470,14 @@ TS_EXPORT int ts_linear_attention(int dtype, const void* q, long long ldq, const
                                   const int* state_slots, const int* fresh, const int* cu_q, int num_requests,
                                   const void* norm_weight, int norm_weight_is_f32, float eps, void* out, long long ldo,
                                   int H, int vdim, int seg_len, float* seg_state, float* seg_decay, int max_segments,
-                                  int num_tokens, float* raw_out, cudaStream_t stream) {
+                                  int num_tokens, float* raw_out, int in_act, int gate_act, int joint_norm,
+                                  cudaStream_t stream) {
   TS_REQUIRE(num_requests > 0 && H > 0 && vdim > 0, "linear_attention: empty input");
   const int cols = block_columns(vdim);
   const int col_tiles = (vdim + cols - 1) / cols;
-  TS_REQUIRE((col_tiles > 1) == (raw_out != nullptr) && num_tokens > 0,
-             "linear_attention: heads of more than %d value columns come with a 32-bit scratch for their outputs, others without",
-             cols);
+  TS_REQUIRE((col_tiles > 1 || joint_norm) == (raw_out != nullptr) && num_tokens > 0,
+             "linear_attention: heads of more than %d value columns, and a norm over all heads, come with a 32-bit scratch "
+             "for their outputs, others without", cols);
   TS_REQUIRE((z != nullptr) != (decay != nullptr), "linear_attention: either per-channel logits or per-head decays");
   TS_REQUIRE(z == nullptr || tau > 0.f, "linear_attention: tau must be positive");
   TS_REQUIRE(rotary_dim >= 0 && rotary_dim <= DIM && rotary_dim % 2 == 0, "linear_attention: rotary_dim %d does not fit key size %d", rotary_dim, DIM);
@@ -465,7 +488,7 @@ TS_EXPORT int ts_linear_attention(int dtype, const void* q, long long ldq, const
              "linear_attention: segments of a multiple of %d tokens with scratch for their states", CHUNK);
   ScanParams p{q, k, v, gate, ldq, ldk, ldv, ldg, z, ldz, decay, z ? 1.f / tau : 0.f, positions, cos, sin, rotary_dim,
                q_scale, k_scale, state, state_slots, fresh, cu_q, norm_weight, norm_weight_is_f32, eps, out, ldo, H, vdim,
-               seg_len, seg_state, seg_decay, max_segments, cols, col_tiles, raw_out};
+               seg_len, seg_state, seg_decay, max_segments, cols, col_tiles, raw_out, in_act, gate_act, joint_norm};
   if (dtype == TS_F32)
     return z ? launch_scan<float, true>(p, num_requests, num_tokens, stream) : launch_scan<float, false>(p, num_requests, num_tokens, stream);
   if (dtype == TS_BF16)

@@ -76,7 +76,7 @@ class ModelRunner:
         self.num_pages = self._size_cache()
         self.device_cache = DeviceCache(self.model, self.num_pages, self.page_size,
                                         cfg.max_num_seqs, self.dtype, self.device)
-        groups = [GroupSpec(s.kind, s.window) for s in self.model.cache_groups]
+        groups = [GroupSpec(s.kind, s.window, s.keep_first) for s in self.model.cache_groups]
         self.manager = CacheManager(groups, self.num_pages, self.page_size, cfg.max_num_seqs)
         self._make_buffers()
         self.graphs: dict = {}

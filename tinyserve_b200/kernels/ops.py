@@ -193,7 +193,7 @@ _NO_SCALE = (c_void_p(0), c_int(0), c_float(0.0))
 
 def materialize(x):
     """An ordinary tensor from what a product, a norm or a block returned."""
-    return x.materialize() if isinstance(x, (SplitPartials, PendingProduct, ScaledRows, PairSum)) else x
+    return x.materialize() if isinstance(x, (SplitPartials, PendingProduct, ScaledRows, PairSum, NormedAddend)) else x
 
 
 def launch_count() -> int:
@@ -496,11 +496,15 @@ def _sampler():
     return build.load_unit("sampler.cu")
 
 
+def _latent_moe():
+    return build.load_unit("latent_moe.cu")
+
+
 def units_for(head_dims, key_dims=()) -> list:
     """The (source, defines) units a model with these attention head sizes, and these key sizes of
     its matrix-state mixers, needs."""
     units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("gemm_tcgen05.cu", {}), ("gemm_pair_tcgen05.cu", {}),
-             ("sampler.cu", {})]
+             ("sampler.cu", {}), ("latent_moe.cu", {})]
     units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
     units += [("attention_mma.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
               if d <= MMA_MAX_HEAD_DIM]
@@ -831,6 +835,12 @@ def attention_backend(dtype, head_dim, page_size=16) -> str:
     return "mma"
 
 
+def attention_backend_with(chosen: str, keep_first: int, has_sinks: bool) -> str:
+    """The kernels that attend when the first keys of a sequence stay visible beside a window, or a
+    sink joins the softmax sum: the 32-bit kernel has both."""
+    return "simt" if (keep_first or has_sinks) else chosen
+
+
 def prefill_tile_queries(dtype, num_heads, num_kv_heads, head_dim, page_size=16) -> int:
     """Queries per block of the prefill kernel that ``attention_backend`` names (0: the kernel
     takes no work list)."""
@@ -843,8 +853,11 @@ def prefill_tile_queries(dtype, num_heads, num_kv_heads, head_dim, page_size=16)
     return 0
 
 
-def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None, backend=None):
+def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None, backend=None, keep_first=0,
+                    sinks=None):
     """Attention of this step's queries over their requests' cached keys and values.
+    ``keep_first`` (with a window): the first keys of a sequence stay visible to every later query.
+    ``sinks`` float32 [H]: head h's softmax sum holds one more term exp(sinks[h]) without key or value.
     q [T, H, D]; caches [pages, Hkv, page_size, D]; ``view`` a GroupView; ``ctx`` gives cu_q,
     kv_lens and the batch's maxima.  bfloat16 runs on the tensor cores (a decode kernel when
     every request brings one token, else a prefill kernel); float32 on the 32-bit kernel.
@@ -854,6 +867,11 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     Hkv = k_cache.shape[1]
     page = view.page_size
     chosen = attention_backend(q.dtype, D, page)
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (H,) or not sinks.is_cuda):
+        raise TypeError("paged_attention: sinks are float32 [heads] on the device")
+    keep_first = int(keep_first) if window > 0 else 0
+    if (keep_first or sinks is not None) and backend is None:
+        backend = attention_backend_with(chosen, keep_first, sinks is not None)
     if backend is not None and backend != chosen:
         if q.dtype != torch.bfloat16 or (backend == "tcgen05") or (backend == "mma" and chosen == "simt"):
             raise ValueError(f"attention backend {backend!r} does not take {q.dtype}, head size {D}, pages of {page}")
@@ -919,7 +937,8 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         c_int(_dt(q)), _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table),
         _ptr(ctx.cu_q), _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len),
         c_int(H), c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)),
-        c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _stream()),
+        c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(keep_first),
+        _ptr(sinks), _stream()),
         launches)
     return out
 
@@ -1260,7 +1279,7 @@ def _linear_attention(key_dim: int):
 
 def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, out_dtype, *, decay=None,
                      decay_logits=None, tau=1.0, rotary=None, q_scale=1.0, k_scale=1.0, norm_weight=None, eps=0.0,
-                     segment=None):
+                     segment=None, input_activation=None, gate_activation="silu", joint_norm=False):
     """Per request and head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over this step's
     tokens, from and to ``state`` [slots, H, key_dim, value_dim] (float32) at the requests' state
     slots (``ctx.state_slots``, ``ctx.fresh``, ``ctx.cu_q``); returns [T, H * value_dim] =
@@ -1268,7 +1287,12 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
     or ``decay_logits`` float32 [T, H * key_dim] with a = sigmoid(z)^(1 / tau).  q, k [T, H key_dim],
     v, gate [T, H value_dim] may be column ranges of one projection.  ``rotary``: positions on q
     and k; ``q_scale`` / ``k_scale``: constant factors (after the rotation).  ``segment``: tokens per
-    segment of the side-by-side form (None: chosen by the step's longest portion, 0: never)."""
+    segment of the side-by-side form (None: chosen by the step's longest portion, 0: never).
+    ``input_activation`` "silu": q, k and v pass through silu first.  ``gate_activation`` "sigmoid":
+    the output is multiplied by sigmoid(gate).  ``joint_norm``: the output norm runs over all heads
+    of a token together, with ``norm_weight`` [H * value_dim]."""
+    if input_activation not in (None, "silu") or gate_activation not in ("silu", "sigmoid"):
+        raise ValueError("linear_attention: input activation None or silu, gate activation silu or sigmoid")
     _cuda(q, k, v, gate, state, decay, decay_logits, norm_weight)
     T = q.shape[0]
     H = num_heads
@@ -1286,7 +1310,7 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
     lib = _linear_attention(key_dim)
     # a head of more value columns than a block takes: its output norm runs as a kernel of its own
     tiles = lib.ts_linear_attention_column_tiles(c_int(value_dim))
-    wide = tiles > 1
+    wide = tiles > 1 or bool(joint_norm)
     if segment is None:
         seg_len = linear_attention_segment(getattr(ctx, "max_q_len", 0), H * tiles,
                                            lib.ts_linear_attention_resident_blocks(c_int(value_dim)))
@@ -1306,5 +1330,145 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
         c_float(q_scale), c_float(k_scale), _ptr(state), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(ctx.cu_q),
         c_int(ctx.num_requests), _ptr(norm_weight), c_int(_vec_flag(norm_weight, out_dtype) if norm_weight is not None else 0),
         c_float(eps), _ptr(out), c_longlong(out.stride(0)), c_int(H), c_int(value_dim), c_int(seg_len), _ptr(seg_state),
-        _ptr(seg_decay), c_int(max_segments), c_int(T), _ptr(raw), _stream()), (3 if seg_len else 1) + int(wide))
+        _ptr(seg_decay), c_int(max_segments), c_int(T), _ptr(raw), c_int(1 if input_activation == "silu" else 0),
+        c_int(1 if gate_activation == "sigmoid" else 0), c_int(1 if joint_norm else 0), _stream()),
+        (3 if seg_len else 1) + int(wide))
     return out
+
+
+# ----------------------------------------------------------------------------- a block that norms what its sub-layers return
+class NormedAddend:
+    """A sub-layer's output that joins the stream through a norm of its own: residual +=
+    y / rms(y) * weight.  The kernel of the next norm does that add while it loads
+    (``normed_add_rmsnorm``); ``materialize()`` gives the normed rows to any other consumer."""
+
+    def __init__(self, y, weight, eps):
+        self.y, self.weight, self.eps = materialize(y), weight, float(eps)
+        self.shape, self.dtype, self.device = tuple(self.y.shape), self.y.dtype, self.y.device
+
+    def materialize(self):
+        return rmsnorm(self.y, self.weight, self.eps)
+
+
+def normed_add_rmsnorm(addend: NormedAddend, residual, weight, eps, out_dtype, rows=None):
+    """residual (float32, in place) += y / rms(y) * w_y; returns residual / rms(residual) * weight as
+    ``out_dtype`` (``weight`` None: only the add).  With ``rows`` (int32) only those rows are added,
+    normalised and returned, and the residual is left as it is."""
+    y = addend.y
+    _cuda(y, addend.weight, residual, weight, rows)
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise TypeError("the residual stream is contiguous float32")
+    if y.dtype != out_dtype or not y.is_contiguous() or y.shape != residual.shape:
+        raise TypeError("normed_add_rmsnorm: the addend is contiguous, of the compute dtype and of the residual's shape")
+    n = residual.shape[1]
+    num_out = residual.shape[0] if rows is None else rows.shape[0]
+    out = torch.empty(num_out, n, dtype=out_dtype, device=residual.device) if weight is not None else None
+    lib = _latent_moe()
+    _check(lib, lib.ts_normed_add_rmsnorm(
+        c_int(_DTYPE[out_dtype]), _ptr(y), _ptr(addend.weight), c_int(_vec_flag(addend.weight, out_dtype)), _ptr(residual),
+        _ptr(weight), c_int(_vec_flag(weight, out_dtype) if weight is not None else 0), c_float(addend.eps), c_float(eps),
+        _ptr(out), _ptr(rows), c_int(num_out), c_int(n), c_int(0 if rows is not None else 1), _stream()))
+    return out
+
+
+# ----------------------------------------------------------------------------- latent attention
+def latent_prepare(proj, q_rank, q_weight, eps, kv_rank=0, rot_dim=0, kv_weight=None, rotary=None, positions=None,
+                   cache=None, slot_mapping=None):
+    """From the fused projection of every token, proj [T, q_rank (+ kv_rank + rot_dim) + ...]: returns
+    the RMS-normed query latent [T, q_rank] and, with ``kv_weight``, writes what the cache keeps of a
+    token to its slot of ``cache`` [pages, 1, page, stored]: the RMS-normed key/value latent, then the
+    shared key part rotated to the token's position, then zeros."""
+    _cuda(proj, q_weight, kv_weight, positions, cache, slot_mapping)
+    T = proj.shape[0]
+    has_kv = kv_weight is not None
+    if proj.stride(1) != 1 or proj.shape[1] < q_rank + (kv_rank + rot_dim if has_kv else 0):
+        raise ValueError("latent_prepare: the projection does not hold the latents")
+    if has_kv and cache is not None and (cache.dtype != proj.dtype or not cache.is_contiguous() or cache.shape[1] != 1):
+        raise TypeError("latent_prepare: the cache is contiguous [pages, 1, page, stored] of the activations' dtype")
+    stored = cache.shape[-1] if cache is not None else kv_rank + rot_dim
+    q_latent = torch.empty(T, q_rank, dtype=proj.dtype, device=proj.device)
+    lib = _latent_moe()
+    _check(lib, lib.ts_latent_prepare(
+        c_int(_dt(proj)), _ptr(proj), c_longlong(proj.stride(0)), c_int(q_rank), c_int(kv_rank), c_int(rot_dim),
+        c_int(stored), c_int(1 if has_kv else 0), _ptr(q_weight), c_int(_vec_flag(q_weight, proj.dtype)), _ptr(kv_weight),
+        c_int(_vec_flag(kv_weight, proj.dtype) if has_kv else 0), c_float(eps), _ptr(positions),
+        _ptr(rotary.cos if rotary is not None else None), _ptr(rotary.sin if rotary is not None else None), _ptr(q_latent),
+        _ptr(cache), _ptr(slot_mapping), c_int(T), _stream()))
+    return q_latent
+
+
+def latent_query(carried, q, num_heads, dim, rot_dim, stored, rotary, positions):
+    """The attention kernel's query rows [T, H, stored]: per head ``carried`` [H, T, kv_rank] (the
+    unrotated query carried into the latent space), then the head's rotated part (columns
+    [dim, dim + rot_dim) of its ``dim + rot_dim`` columns of q [T, H (dim + rot_dim)]) turned to the
+    token's position, then zeros."""
+    _cuda(carried, q, positions)
+    H, T, kv_rank = carried.shape
+    if H != num_heads or not carried.is_contiguous() or q.stride(1) != 1 or q.shape != (T, H * (dim + rot_dim)):
+        raise ValueError("latent_query: operands do not fit")
+    out = torch.empty(T, H, stored, dtype=q.dtype, device=q.device)
+    lib = _latent_moe()
+    _check(lib, lib.ts_latent_query(
+        c_int(_dt(q)), _ptr(carried), _ptr(q), c_longlong(q.stride(0)), c_int(H), c_int(dim), c_int(rot_dim), c_int(kv_rank),
+        c_int(stored), _ptr(positions), _ptr(rotary.cos if rotary is not None else None),
+        _ptr(rotary.sin if rotary is not None else None), _ptr(out), c_int(T), _stream()))
+    return out
+
+
+def gate_heads(x, gate):
+    """[T, H * n] = x [H, T, n] * sigmoid(gate [T, H * n]); ``gate`` may be a column range."""
+    _cuda(x, gate)
+    H, T, n = x.shape
+    if not x.is_contiguous() or gate.shape != (T, H * n) or gate.stride(1) != 1 or gate.dtype != x.dtype:
+        raise ValueError("gate_heads: operands do not fit")
+    out = torch.empty(T, H * n, dtype=x.dtype, device=x.device)
+    lib = _latent_moe()
+    _check(lib, lib.ts_gate_heads(c_int(_dt(x)), _ptr(x), _ptr(gate), c_longlong(gate.stride(0)), _ptr(out), c_int(H), c_int(n),
+                                  c_int(T), _stream()))
+    return out
+
+
+def batched_matmul(a, b):
+    """[B, M, N] = a [B, M, K] @ b [B, K, N], any strides, 32-bit sums.  bfloat16 operands go to the
+    library's batched product (as the plain products of many rows do); float32 operands to this
+    package's FMA kernel."""
+    _cuda(a, b)
+    B, M, K = a.shape
+    if b.shape[0] != B or b.shape[1] != K or a.dtype != b.dtype:
+        raise ValueError(f"batched_matmul: {tuple(a.shape)} does not fit {tuple(b.shape)}")
+    if a.dtype == torch.bfloat16:
+        return torch.bmm(a, b)
+    N = b.shape[2]
+    out = torch.empty(B, M, N, dtype=a.dtype, device=a.device)
+    lib = _latent_moe()
+    _check(lib, lib.ts_batched_matmul(
+        c_int(_dt(a)), _ptr(a), c_longlong(a.stride(0)), c_longlong(a.stride(1)), c_longlong(a.stride(2)), _ptr(b),
+        c_longlong(b.stride(0)), c_longlong(b.stride(1)), c_longlong(b.stride(2)), _ptr(out), c_int(B), c_int(M), c_int(N),
+        c_int(K), _stream()))
+    return out
+
+
+# ----------------------------------------------------------------------------- mixture of experts
+def moe_route(logits, top):
+    """float32 [T, E] router logits -> float32 [T, E]: softmax over all experts, the ``top`` largest
+    keep their probability as it is, the others become zero."""
+    _cuda(logits)
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise TypeError("moe_route: router logits are contiguous float32")
+    T, E = logits.shape
+    gates = torch.empty_like(logits)
+    lib = _latent_moe()
+    _check(lib, lib.ts_moe_route(_ptr(logits), _ptr(gates), c_int(T), c_int(E), c_int(top), _stream()))
+    return gates
+
+
+def moe_activate_(a, gates, num_experts):
+    """a [T, E * ff] (in place) <- relu(a)^2 * gates[t, e] for the columns of expert e."""
+    _cuda(a, gates)
+    T = a.shape[0]
+    if not a.is_contiguous() or a.shape[1] % num_experts or gates.shape != (T, num_experts) or gates.dtype != torch.float32:
+        raise ValueError("moe_activate: operands do not fit")
+    lib = _latent_moe()
+    _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), _ptr(gates), c_int(T), c_int(num_experts),
+                                    c_int(a.shape[1] // num_experts), _stream()))
+    return a

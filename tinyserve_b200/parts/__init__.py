@@ -6,8 +6,10 @@ from .norm import LayerNorm, RMSNorm
 from .rotary import Rotary
 from .attention import Attention
 from .mlp import GatedMLP
-from .linear_attention import GatedLinearAttention, Retention
+from .linear_attention import GatedLinearAttention, Lightning, Retention
+from .latent_attention import LatentAttention
+from .moe import MixtureOfExperts
 from .side_by_side import SideBySide
 from .stream import InputInjection
-from .block import ARRANGEMENTS, ParallelBlock, PreNormBlock, build_block
+from .block import ARRANGEMENTS, ParallelBlock, PreNormBlock, SandwichBlock, build_block
 from .model import BoundCall, DecoderModel, Embedding, LMHead, build_model

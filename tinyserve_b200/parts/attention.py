@@ -14,7 +14,10 @@ divided by their root mean square per head, without a weight, after the position
 projection of the same input (``head_gate``, rows of the fused projection after v).  With any
 of these the heads are stored ``stored_dim`` wide (the larger of the two head sizes, rounded up
 to what the attention kernels take), padded with zeros: zero key columns add nothing to a score
-and the padded output columns are dropped."""
+and the padded output columns are dropped.
+
+With a window, ``keep_first`` > 0 keeps the first tokens of every sequence visible to all later
+queries (they keep their own positions, and their pages are never released)."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -32,7 +35,7 @@ class Attention(Mixer):
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, bias=False, qk_norm=None,
                  position=None, window=0, scale=None, names=None, value_dim=None, unit_norm_eps=None,
-                 head_gate=False):
+                 head_gate=False, keep_first=0):
         super().__init__()
         self.names = dict(DEFAULT_NAMES, **(names or {}))
         if num_heads % num_kv_heads:
@@ -46,9 +49,13 @@ class Attention(Mixer):
         self.value_dim = int(value_dim) if value_dim else head_dim
         self.unit_norm_eps = None if unit_norm_eps is None else float(unit_norm_eps)
         self.head_gate = bool(head_gate)
+        self.keep_first = int(keep_first or 0) if self.window > 0 else 0
+        if self.keep_first < 0:
+            raise ValueError("attention: keep_first must not be negative")
         #: the plain form runs the kernels that fuse per-head norm, rotary and cache write (and, for
         #: a few decoded tokens, the attention itself); the general form has kernels of its own
-        self.general = self.value_dim != head_dim or self.unit_norm_eps is not None or self.head_gate
+        self.general = (self.value_dim != head_dim or self.unit_norm_eps is not None or self.head_gate
+                        or self.keep_first > 0)
         if self.general and (qk_norm is not None or bias):
             raise ValueError("attention: a value size of its own, the unit norm and the head gate come "
                              "without a weighted q/k norm and without biases")
@@ -87,11 +94,14 @@ class Attention(Mixer):
 
     def cache_spec(self):
         kind = "window" if self.window > 0 else "full"
-        return CacheSpec(kind, self.num_kv_heads, self.stored_dim, self.window)
+        return CacheSpec(kind, self.num_kv_heads, self.stored_dim, self.window, keep_first=self.keep_first)
 
     accepts_scaled_rows = True
 
     def work_tile_queries(self, dtype, page_size):
+        backend = ops.attention_backend(dtype, self.stored_dim, page_size)
+        if ops.attention_backend_with(backend, self.keep_first, False) == "simt":
+            return 0
         return ops.prefill_tile_queries(dtype, self.num_heads, self.num_kv_heads, self.stored_dim, page_size)
 
     def _forward_general(self, h, ctx, call):
@@ -105,7 +115,7 @@ class Attention(Mixer):
             self.num_kv_heads, self.head_dim, self.value_dim, self.stored_dim, rotary=self.position,
             unit_norm=self.unit_norm_eps is not None, eps=self.unit_norm_eps or 0.0, k_cache=cache.k, v_cache=cache.v,
             slot_mapping=view.slot_mapping if call.writes_cache else None, page_size=view.page_size)
-        out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window)
+        out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window, keep_first=self.keep_first)
         if self.head_gate or self.stored_dim != self.value_dim:
             out = ops.head_gate(out, qkv[:, v_end:] if self.head_gate else None, self.value_dim)
         else:

@@ -34,7 +34,7 @@ class ParamSpec:
     role "vector": small per-channel tensor; kept in the engine's dtype, but a
     tensor that the checkpoint stores in 32-bit stays 32-bit.
     role "int_table": integer table, kept as int32.
-    init: "normal" (N(0, 0.02)), "norm_weight" (1 + U(-0.1, 0.1)) or "zeros", used by
+    init: "normal" (N(0, 0.02)), "norm_weight" (1 + U(-0.1, 0.1)), "around_zero" (U(-0.1, 0.1)) or "zeros", used by
     the random-weights mode.  ``sources`` lists the checkpoint tensors that fill it
     (default: one tensor of the same name and shape).  ``interleave_halves`` = b > 0: after the
     sources are placed, the rows of the first and the second half alternate in blocks of b rows
@@ -79,6 +79,7 @@ class CacheSpec:
     head_dim: int = 0
     window: int = 0
     tensors: tuple = ()
+    keep_first: int = 0      # "window": the first tokens of a sequence that stay visible, and kept, for good
 
     def __post_init__(self):
         if not self.tensors:

@@ -3,7 +3,8 @@
 "pre_norm" is tinyserve's decoder layer (serve.py:1177-1181): the stream travels as
 (x, residual); each norm first adds x to the residual, then normalises it; the
 sub-layer's output becomes the next x, so that r1 = r0 + mixer(norm1(r0)),
-r2 = r1 + ffn(norm2(r1)).  Another arrangement is another class in ARRANGEMENTS.
+r2 = r1 + ffn(norm2(r1)).  Another arrangement is another class in ARRANGEMENTS ("parallel": mixer
+and feed-forward side by side on one norm; "sandwich": a norm before and after each sub-layer).
 
 The block also owns what lies below the parts' interfaces: a product may hand its result on
 unfinished (split-K partial tiles, a product that has not run yet, rows without their norm
@@ -24,6 +25,9 @@ def add_and_norm(norm, x, residual, reader=None, rows=None, compute_dtype=None):
     (``accepts_scaled_rows``) may get rows without their norm factor; any other norm gets a
     finished tensor."""
     rms = norm.rms_parameters()
+    if isinstance(x, ops.NormedAddend) and rms is not None:
+        # the norm on the sub-layer's output, the add and this norm are one kernel
+        return ops.normed_add_rmsnorm(x, residual, rms[0], rms[1], compute_dtype or x.dtype, rows=rows)
     if rms is None:
         return norm.add_forward(x if norm.takes_pending else ops.materialize(x), residual, rows=rows)
     weight, eps = rms
@@ -102,7 +106,50 @@ class ParallelBlock(Part):
         return ops.PairSum(mixed, self.ffn.forward(h, ctx) if self.ffn is not None else None)
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock}
+class SandwichBlock(Part):
+    """A norm before and after each sub-layer: r <- r + post1(mixer(pre1(r))), then
+    r <- r + post2(ffn(pre2(r))).  What a sub-layer returns travels on with its post-norm
+    (``ops.NormedAddend``); the kernel of the next pre-norm (the next block's, or the model's final
+    norm) norms it, adds it to the 32-bit residual and norms the sum.  A layer without a
+    feed-forward (``LayerSpec.ffn`` None) has the first line only."""
+    capturable = True
+
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        super().__init__()
+        self.mixer = build_mixer(spec.mixer)
+        self.ffn = build_feed_forward(spec.ffn) if spec.ffn is not None else None
+        self.input_norm = build_norm(spec.norm, hidden_size)
+        self.mixer_out_norm = build_norm(spec.norm, hidden_size)
+        self.post_mixer_norm = build_norm(spec.norm, hidden_size) if self.ffn is not None else None
+        self.ffn_out_norm = build_norm(spec.norm, hidden_size) if self.ffn is not None else None
+        for norm in (self.input_norm, self.mixer_out_norm, self.post_mixer_norm, self.ffn_out_norm):
+            if norm is not None and not hasattr(norm, "eps"):
+                raise ValueError("sandwich block: its norms are RMS norms")
+        self._names = {"mixer": spec.name_of("mixer", self.mixer.tree_name),
+                       "ffn": spec.name_of("ffn", self.ffn.tree_name if self.ffn is not None else ""),
+                       "input_norm": spec.name_of("input_norm"),
+                       "mixer_out_norm": spec.name_of("mixer_out_norm", "post_mixer_out_layernorm"),
+                       "post_mixer_norm": spec.name_of("post_mixer_norm"),
+                       "ffn_out_norm": spec.name_of("ffn_out_norm", "post_feedforward_layernorm")}
+
+    def children(self):
+        n = self._names
+        out = {n["mixer"]: self.mixer, n["input_norm"]: self.input_norm, n["mixer_out_norm"]: self.mixer_out_norm}
+        if self.ffn is not None:
+            out.update({n["ffn"]: self.ffn, n["post_mixer_norm"]: self.post_mixer_norm,
+                        n["ffn_out_norm"]: self.ffn_out_norm})
+        return out
+
+    def forward(self, x, residual, ctx, call):
+        h = ops.materialize(add_and_norm(self.input_norm, x, residual, None, compute_dtype=ctx.dtype))
+        mixed = ops.NormedAddend(self.mixer.forward(h, ctx, call), *self.mixer_out_norm.rms_parameters())
+        if self.ffn is None:
+            return mixed
+        h = ops.materialize(add_and_norm(self.post_mixer_norm, mixed, residual, None, compute_dtype=ctx.dtype))
+        return ops.NormedAddend(self.ffn.forward(h, ctx), *self.ffn_out_norm.rms_parameters())
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock, "sandwich": SandwichBlock}
 
 
 def build_block(spec: LayerSpec, hidden_size: int):

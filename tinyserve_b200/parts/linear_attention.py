@@ -12,6 +12,10 @@ the value size, silu gate, output projection) is ``MatrixStateMixer``; they diff
   z = W2 (W1 h) + b a low-rank projection of the mixer's input, q times key_dim^(-1/2), a weight
   of value size on the output norm (one for all heads).
 
+* ``Lightning``: one constant decay per head (a list), silu on q, k and v, no positions and no
+  factor; the heads of a token are normed together with one weight over all of them and multiplied
+  by sigmoid (not silu) of the gate.
+
 Everything behind the projections is 32-bit (angles, decays, state, output norm):
 csrc/linear_attention.cu.  The decay logits z leave their product in 32-bit."""
 from __future__ import annotations
@@ -120,5 +124,31 @@ class GatedLinearAttention(MatrixStateMixer):
         return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
 
 
+class Lightning(MatrixStateMixer):
+    def __init__(self, hidden_size, num_heads, key_dim, value_dim, decay, eps, names=None):
+        super().__init__(hidden_size, num_heads, key_dim, value_dim, eps, names)
+        self.decay_values = tuple(float(d) for d in decay)
+        if len(self.decay_values) != num_heads:
+            raise ValueError(f"lightning: {len(self.decay_values)} decays for {num_heads} heads")
+        self.decay = None
+
+    def param_specs(self):
+        specs = super().param_specs()
+        specs["norm.weight"] = ParamSpec((self.v_size,), role="vector", init="norm_weight",
+                                         sources=(Source(f"{self.names['norm']}.weight", 0, self.v_size),))
+        return specs
+
+    def prepare(self, runtime):
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=runtime.device)
+
+    def forward(self, h, ctx, call):
+        _, q, k, v, g = self._split(h)
+        out = ops.linear_attention(q, k, v, g, ctx.state(call.state), ctx, self.num_heads, self.key_dim,
+                                   self.value_dim, ctx.dtype, decay=self.decay, norm_weight=self.w["norm.weight"],
+                                   eps=self.eps, input_activation="silu", gate_activation="sigmoid", joint_norm=True)
+        return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
+
+
 register_mixer("retention", Retention)
+register_mixer("lightning", Lightning)
 register_mixer("gated_linear_attention", GatedLinearAttention)

@@ -11,17 +11,25 @@ from .base import Norm, ParamSpec, register_norm
 class RMSNorm(Norm):
     capturable = True
 
-    def __init__(self, dim: int, eps: float):
+    def __init__(self, dim: int, eps: float, offset: float = 0.0):
+        """``offset``: the checkpoint stores the weight as its distance from ``offset`` (a weight kept
+        around zero has offset 1); the sum is made once, in 32-bit, when the tensor is bound."""
         super().__init__()
         self.dim = dim
         self.eps = float(eps)
+        self.offset = float(offset)
         self.compute_dtype = None
+
+    def bind(self, tensors):
+        if self.offset and "weight" in tensors:
+            tensors = dict(tensors, weight=(tensors["weight"].float() + self.offset).contiguous())
+        super().bind(tensors)
 
     def prepare(self, runtime):
         self.compute_dtype = runtime.dtype
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.dim,), role="vector", init="norm_weight")}
+        return {"weight": ParamSpec((self.dim,), role="vector", init="around_zero" if self.offset else "norm_weight")}
 
     def forward(self, x, out=None):
         return ops.rmsnorm(x, self.w["weight"], self.eps, out=out)

@@ -1,7 +1,8 @@
 """Random weights: write a model folder from a configuration and a seed, or fill a
 model on the device directly (for measurements at sizes one would not write to disk).
 
-Distribution: matrices and embeddings N(0, 0.02), norm weights 1 + U(-0.1, 0.1),
+Distribution: matrices and embeddings N(0, 0.02), norm weights 1 + U(-0.1, 0.1) (U(-0.1, 0.1) where
+the checkpoint keeps them around zero),
 "zeros" parameters 0.  tinyserve has no such mode; it always loads a checkpoint
 (serve.py:1289-1404)."""
 from __future__ import annotations
@@ -22,6 +23,8 @@ def _draw(init: str, shape, generator, device="cpu"):
         return torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=generator)
     if init == "norm_weight":
         return 1.0 + torch.empty(shape, dtype=torch.float32, device=device).uniform_(-0.1, 0.1, generator=generator)
+    if init == "around_zero":
+        return torch.empty(shape, dtype=torch.float32, device=device).uniform_(-0.1, 0.1, generator=generator)
     if init == "zeros":
         return torch.zeros(shape, dtype=torch.float32, device=device)
     raise ValueError(f"unknown init {init!r}")
