@@ -201,3 +201,19 @@ def forward(cfg, W, tokens, return_layers=False):
         streams.append(x)
     logits = norm_around_zero(x, W["final.norm"], eps) @ W["embed"].T
     return (logits, torch.stack(streams)) if return_layers else logits
+
+
+def logits(cfg, W, tokens):
+    return forward(cfg, W, tokens)
+
+
+def greedy(cfg, W, prompt, n):
+    """n greedy tokens after ``prompt``; with each, the gap between the best and the second logit."""
+    ids, out, gaps = list(prompt), [], []
+    for _ in range(n):
+        row = forward(cfg, W, ids)[-1]
+        best = torch.topk(row, 2)
+        out.append(int(best.indices[0]))
+        gaps.append(float(best.values[0] - best.values[1]))
+        ids.append(out[-1])
+    return out, gaps
