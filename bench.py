@@ -19,6 +19,11 @@ The engine runs on one GPU; with --gpus > 1 it says so and exits with 2.
 measures another design beside Qwen3 at equal size instead (random weights, same width, block
 runs, feed-forward width, heads and vocabulary): prefill of one 2,048-token prompt, decode at
 batch 8, and the design's own kernels beside the like kernels of Qwen3, each against its roofline.
+
+    python bench.py --arch delilorn [--sizes 2048,4096]
+
+does the same for Delilorn (latent attention, lightning attention, attention over a window beside
+kept first tokens, a mixture of experts whose active weights equal Qwen3's feed-forward).
 """
 from __future__ import annotations
 
@@ -354,6 +359,32 @@ def dudatar_shapes(width):
     return dudatar, qwen3
 
 
+def delilorn_shapes(width):
+    """A Delilorn of real layer sizes at ``width``: latent attention, lightning, latent attention on
+    the first layer's cache, attention over a window of 1,024 beside 4 kept tokens, lightning,
+    window attention: six blocks, each with 8 experts of which a token takes 2, sized so that a
+    token's active expert weights equal the feed-forward of the Qwen3 beside it (same width, block
+    count, attention heads and vocabulary)."""
+    heads, ff, vocab = width // 128, width * 11 // 4, 32768
+    ffe = (3 * ff // 4 + 63) // 64 * 64             # 2 experts x 2 matrices = 3 matrices of the gated feed-forward
+    moe = {"kind": "moe", "expert": {"ff": ffe}, "router": {"experts": 8, "top": 2}}
+    rank, rot = (96, 32) if width < 4096 else (192, 64)          # cache rows of 128 and of 256
+    latent = {"heads": heads, "dim": 128, "rot_dim": rot, "vdim": 128, "q_rank": width // 2, "kv_rank": rank,
+              "scale": (128 + rot) ** -0.5, "rot": {"base": 1e4, "dims": rot}}
+    lightning = {"heads": heads // 2, "dim": 128, "vdim": 256,
+                 "decay": [1.0 - 2.0 ** -(5 + 5 * i / max(1, heads // 2 - 1)) for i in range(heads // 2)]}
+    window = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+              "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+              "mask": {"size": 1024, "keep_first": 4}}
+    layer = lambda kind, mixer: {"type": kind, "mixer": mixer, "mlp": moe}
+    delilorn = {"architecture": "Delilorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": [
+        layer("latent_attention", latent), layer("lightning", lightning), layer("latent_attention", dict(latent, kv_from=0)),
+        layer("attention", window), layer("lightning", lightning), layer("attention", window)]}
+    qwen3 = dict(QWEN3_8B, hidden_size=width, num_hidden_layers=6, num_attention_heads=heads,
+                 num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=ff, vocab_size=vocab)
+    return delilorn, qwen3
+
+
 def _time_us(fn, iters=20):
     import torch
     for _ in range(3):
@@ -435,8 +466,121 @@ def kernel_table(width, peaks):
     return out
 
 
+def delilorn_kernel_table(width, peaks):
+    """Delilorn's kernels beside the like kernels of Qwen3 at this width, one launch each, time over
+    roofline time: attention over one latent head with a sink (prefill FLOPs over the library's GEMM
+    rate; decode bytes of the cache rows, read once for keys and values alike), attention over a window
+    beside kept tokens (the FLOPs and bytes of the visible keys only), the lightning form of the
+    matrix-state scan, the experts (the FLOPs of the chosen experts; at decode the bytes of all experts'
+    weights), and the norm that norms a sub-layer's output, adds it and norms the sum."""
+    import torch
+    from types import SimpleNamespace
+    from tinyserve_b200.engine.batch import GroupView, StepContext
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.parts.moe import MixtureOfExperts
+    dev, bf = "cuda:0", torch.bfloat16
+    raw, _ = delilorn_shapes(width)
+    lat, lig, win = (raw["layers"][i]["mixer"] for i in (0, 1, 3))
+    moe = raw["layers"][0]["mlp"]
+    heads = lat["heads"]
+    fma_tflops = ops.num_sms() * 128 * 2 * 1.965e9 / 1e12
+    out = {}
+
+    def frac(key, us, roof):
+        out[key] = {"us": round(us, 1), "roofline_us": round(roof, 2), "frac": round(roof / us, 3)}
+
+    for name, lengths, starts in (("prefill_2048", [2048], [0]), ("decode_b8", [1] * 8, [2048] * 8)):
+        T, B = sum(lengths), len(lengths)
+        kv_len, page = starts[0] + lengths[0], 64
+        pages_per = -(-kv_len // page)
+        cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=dev)
+        table = (torch.arange(B * pages_per, dtype=torch.int32, device=dev) + 1).view(B, pages_per)
+
+        def context():
+            sc = StepContext()
+            sc.num_tokens, sc.num_requests, sc.max_q_len, sc.max_kv_len = T, B, max(lengths), kv_len
+            sc.cu_q, sc.kv_lens = cu, torch.full((B,), kv_len, dtype=torch.int32, device=dev)
+            sc.host = {"cu_q": cu.tolist(), "kv_lens": [kv_len] * B}
+            return sc
+
+        def attention(H, G, D, window=0, keep=0, sinks=None, shared=False):
+            kc = torch.randn(B * pages_per + 1, G, page, D, device=dev).to(bf)
+            vc = kc if shared else torch.randn_like(kc)
+            view = GroupView(page, pages_per, None, table, kc.shape[0])
+            q = torch.randn(T, H, D, device=dev).to(bf)
+            sc = context()
+            return _time_us(lambda: ops.paged_attention(q, kc, vc, view, sc, D ** -0.5, window, keep_first=keep, sinks=sinks))
+
+        def visible(window, keep):
+            pos = torch.arange(kv_len - lengths[0], kv_len)
+            seen = pos + 1 if not window else torch.minimum(pos + 1, torch.full_like(pos, window)) + torch.clamp(
+                torch.minimum(pos + 1 - window, torch.full_like(pos, keep)), min=0)
+            return float(seen.sum())
+
+        def attention_roof(H, G, D, window=0, keep=0, tensors=2):
+            if T > B:
+                return 4.0 * H * D * visible(window, keep) / (peaks["bf16_tflops"] * 1e6)
+            return B * visible(window, keep) * tensors * G * D * 2 / (peaks["hbm_gbs"] * 1e3)
+
+        D = -(-(lat["kv_rank"] + lat["rot_dim"]) // 16) * 16
+        sinks = torch.randn(heads, device=dev)
+        frac(f"latent_attention_{name}", attention(heads, 1, D, sinks=sinks, shared=True), attention_roof(heads, 1, D, tensors=1))
+        G = win["kv_heads"]
+        frac(f"window_attention_{name}", attention(heads, G, 128, win["mask"]["size"], win["mask"]["keep_first"]),
+             attention_roof(heads, G, 128, win["mask"]["size"], win["mask"]["keep_first"]))
+        frac(f"qwen3_attention_{name}", attention(heads, G, 128), attention_roof(heads, G, 128))
+        # the scan: lightning form beside the retention form (the same kernel)
+        H, n, nv = lig["heads"], lig["dim"], lig["vdim"]
+        ctx = SimpleNamespace(num_requests=B, cu_q=cu, max_q_len=max(lengths),
+                              state_slots=torch.arange(B, dtype=torch.int32, device=dev),
+                              fresh=torch.zeros(B, dtype=torch.int32, device=dev),
+                              positions=torch.cat([torch.arange(s, s + m) for s, m in zip(starts, lengths)]).int().to(dev))
+        proj = torch.randn(T, 2 * H * n + 2 * H * nv, device=dev).to(bf)
+        q, k, v, g = proj[:, :H * n], proj[:, H * n:2 * H * n], proj[:, 2 * H * n:2 * H * n + H * nv], proj[:, 2 * H * n + H * nv:]
+        state = torch.zeros(B, H, n, nv, device=dev)
+        decay = torch.full((H,), 0.99, device=dev)
+        wj = torch.ones(H * nv, device=dev)
+        roof = max((T * (2 * H * n + 3 * H * nv) * 2 + 2 * B * H * n * nv * 4) / (peaks["hbm_gbs"] * 1e3),
+                   4.0 * T * H * n * nv / (fma_tflops * 1e6))
+        frac(f"lightning_scan_{name}", _time_us(lambda: ops.linear_attention(
+            q, k, v, g, state, ctx, H, n, nv, bf, decay=decay, norm_weight=wj, eps=1e-6, input_activation="silu",
+            gate_activation="sigmoid", joint_norm=True)), roof)
+        frac(f"retention_scan_{name}", _time_us(lambda: ops.linear_attention(
+            q, k, v, g, state, ctx, H, n, nv, bf, decay=decay, k_scale=n ** -0.5, eps=1e-6)), roof)
+        # the experts beside the gated feed-forward of equal active weights
+        E, top, ffe, ff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"], width * 11 // 4
+        part = MixtureOfExperts(width, ffe, E, top)
+        part.bind({"router.weight": (torch.randn(E, width, device=dev) * 0.1).to(bf),
+                   "up.weight": (torch.randn(E * ffe, width, device=dev) * 0.02).to(bf),
+                   "down.weight": (torch.randn(E * width, ffe, device=dev) * 0.02).to(bf)})
+        h = torch.randn(T, width, device=dev).to(bf)
+        gate_up = (torch.randn(2 * ff, width, device=dev) * 0.02).to(bf)
+        down = (torch.randn(width, ff, device=dev) * 0.02).to(bf)
+        block = ops.GATED_BLOCK if ff % ops.GATED_BLOCK == 0 else 0
+        us_moe = _time_us(lambda: ops.materialize(part.forward(h, None)))
+        us_mlp = _time_us(lambda: ops.materialize(ops.linear(ops.gated_linear(h, gate_up, "silu", block), down)))
+        if T > B:
+            frac(f"experts_{name}", us_moe, 4.0 * T * top * width * ffe / (peaks["bf16_tflops"] * 1e6))
+            frac(f"qwen3_feed_forward_{name}", us_mlp, 6.0 * T * width * ff / (peaks["bf16_tflops"] * 1e6))
+        else:
+            frac(f"experts_{name}", us_moe, 2.0 * E * width * ffe * 2 / (peaks["hbm_gbs"] * 1e3))
+            frac(f"qwen3_feed_forward_{name}", us_mlp, 3.0 * width * ff * 2 / (peaks["hbm_gbs"] * 1e3))
+        # the norms
+        res = torch.randn(T, width, device=dev)
+        y = torch.randn(T, width, device=dev).to(bf)
+        wn = torch.ones(width, device=dev)
+        frac(f"normed_add_rmsnorm_{name}", _time_us(lambda: ops.normed_add_rmsnorm(ops.NormedAddend(y, wn, 1e-6), res, wn, 1e-6, bf)),
+             T * width * (8 + 2 + 2) / (peaks["hbm_gbs"] * 1e3))
+        frac(f"add_rmsnorm_{name}", _time_us(lambda: ops.add_rmsnorm(y, res, wn, 1e-6, bf)),
+             T * width * (8 + 2 + 2) / (peaks["hbm_gbs"] * 1e3))
+    return out
+
+
+ARCH_BENCHES = {"dudatar": (dudatar_shapes, kernel_table), "delilorn": (delilorn_shapes, delilorn_kernel_table)}
+
+
 def arch_main(a) -> int:
-    """``--arch dudatar``: the design beside Qwen3 at equal size.  One JSON line."""
+    """``--arch dudatar`` / ``--arch delilorn``: the design beside Qwen3 at equal size.  One JSON line."""
     import torch
     from tinyserve_b200 import LLM
     from tinyserve_b200.config import config_from_dict
@@ -445,7 +589,8 @@ def arch_main(a) -> int:
     sizes = {}
     for width in [int(w) for w in a.sizes.split(",")]:
         entry = {}
-        for name, raw in zip(("dudatar", "qwen3"), dudatar_shapes(width)):
+        shapes, table = ARCH_BENCHES[a.arch]
+        for name, raw in zip((a.arch, "qwen3"), shapes(width)):
             llm = LLM(model_config=config_from_dict(raw), random_weights=True, dtype="bfloat16", max_model_len=CONTEXT,
                       block_size=a.block_size, max_num_seqs=8, max_num_batched_tokens=PREFILL_TOKENS,
                       num_blocks=8 * (CONTEXT // a.block_size) // 2 + 4096 // a.block_size, use_cuda_graphs=False, seed=a.seed)
@@ -458,9 +603,9 @@ def arch_main(a) -> int:
                            "weight_gib": round(llm.runner.weight_bytes / 2 ** 30, 3)}
             _release(llm)
             llm = None
-        entry["kernels"] = kernel_table(width, peaks)
+        entry["kernels"] = table(width, peaks)
         sizes[str(width)] = entry
-    print(json.dumps({"metric": "prefill and decode tok/s, Dudatar beside Qwen3 at equal size (random weights)",
+    print(json.dumps({"metric": f"prefill and decode tok/s, {a.arch.capitalize()} beside Qwen3 at equal size (random weights)",
                       "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "steps": steps,
                       "warmup": warmup, "block_runs": 6, "sizes": sizes, "peaks": peaks}))
     return 0
@@ -504,13 +649,13 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the 0.6B burst, the 32B run and the long-context decode")
-    ap.add_argument("--arch", choices=["qwen3", "dudatar"], default="qwen3",
-                    help="dudatar: measure that design beside Qwen3 at equal size instead of the default workload")
-    ap.add_argument("--sizes", default="2048,4096", help="--arch dudatar: model widths to measure")
+    ap.add_argument("--arch", choices=["qwen3", "dudatar", "delilorn"], default="qwen3",
+                    help="dudatar, delilorn: measure that design beside Qwen3 at equal size instead of the default workload")
+    ap.add_argument("--sizes", default="2048,4096", help="--arch dudatar / delilorn: model widths to measure")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_main(a)
-    if a.arch == "dudatar":
+    if a.arch in ARCH_BENCHES:
         if a.gpus != 1:
             print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
             return 2

@@ -73,9 +73,23 @@ def delilorn_config(name: str):
     return config_from_dict(delilorn_config_dict(name))
 
 
+def decisive_routers(folder: str, factor: float = 10.0) -> str:
+    """The routers of a random model multiplied by ``factor``: with weights of 0.02 all experts score
+    alike, and which of them a token takes would hang on the last bit of a sum."""
+    import os
+    from safetensors.torch import load_file, save_file
+    path = os.path.join(folder, "model.safetensors")
+    weights = load_file(path)
+    for name in weights:
+        if name.endswith(".router"):
+            weights[name] = (weights[name].float() * factor).to(weights[name].dtype)
+    save_file(weights, path)
+    return folder
+
+
 def make_delilorn_dir(folder, name: str, seed: int = 0) -> str:
     from tinyserve_b200.weights import write_random_model
-    return write_random_model(delilorn_config(name), str(folder), seed=seed)
+    return decisive_routers(write_random_model(delilorn_config(name), str(folder), seed=seed))
 
 
 def random_delilorn_config_dict(seed: int) -> dict:

@@ -13,8 +13,10 @@
 // Scores, running maxima, sums and the output accumulate in 32-bit; exp2 with scale * log2(e);
 // the probabilities are rounded to bfloat16 for P * V, as tinykernels.py:386-413 and 993 do.
 // Visibility as serve.py:668-680: key j is seen by the query at position p iff j <= p and, with a
-// window W > 0, j > p - W.  Keys are found through the block table; the cache layout is
-// [page, kv_head, slot, head_dim].
+// window W > 0, j > p - W or j < keep_first (the first keys of a sequence may stay visible to all
+// later queries: the walk over the key tiles then starts with the tiles that hold them).  With
+// `sinks`, head h's softmax sum holds one more term exp(sinks[h]) that has no key and no value.
+// Keys are found through the block table; the cache layout is [page, kv_head, slot, head_dim].
 #include "tcgen05.cuh"
 
 #ifndef TS_HEAD_DIM
@@ -56,6 +58,8 @@ struct MmaAttnParams {
   int H, Hkv, page_shift, page_mask, max_blocks;
   int heads_per_tile, queries_per_tile, head_tiles;
   int num_splits, window;
+  int keep_first;           // with a window: keys below this stay visible
+  const float* sinks;       // [H] or null
   float scale_log2;
   // Decode straight from the fused q/k/v projection (from_qkv != 0; q is not read): every block
   // builds its query rows itself (sum of the split-K partial tiles, per-head RMSNorm, rotary), and
@@ -108,14 +112,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// NKEYS keys from j0 on -> shared memory (keys and values); keys outside [j_lo, j_hi) become zeros
+// NKEYS keys from j0 on -> shared memory (keys and values); keys outside [j_lo, j_hi) and not below `keep` become zeros
 template <int NKEYS, int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(char* ks, char* vs, const MmaAttnParams& p, const int* bt,
-                                             int kvh, int j0, int j_lo, int j_hi) {
+                                             int kvh, int j0, int j_lo, int j_hi, int keep = 0) {
   for (int i = threadIdx.x; i < NKEYS * CH; i += NTHREADS) {
     const int key = i / CH, c = i % CH;
     const int j = j0 + key;
-    const bool valid = j >= j_lo && j < j_hi;
+    const bool valid = (j >= j_lo || j < keep) && j < j_hi;
     size_t off = 0;
     if (valid) {
       const size_t page = bt[j >> p.page_shift];
@@ -187,13 +191,13 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[N
 
 // Online softmax of one tile for the two rows a lane holds (g and g + 8 of the warp's 16).
 // s holds raw scores on entry and probabilities on exit.  `jbase` is the position of column 0.
-// pos[h] is the position of row h's query, lo[h] the lowest visible key; a row with pos < 0 sees
-// nothing.
+// pos[h] is the position of row h's query, lo[h] the lowest visible key of its window (keys below
+// `keep` are visible besides); a row with pos < 0 sees nothing.
 // MASK false: every key of the tile is visible to both rows (no comparisons).
 template <int NT, bool MASK = true>
 __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8][4], float (&m)[2],
                                              float (&l)[2], const int (&pos)[2], const int (&lo)[2],
-                                             int jbase, float scale_log2, int lane) {
+                                             int jbase, float scale_log2, int lane, int keep = 0) {
   const int t = lane & 3;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -203,7 +207,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = jbase + nt * 8 + 2 * t + e;
-        const bool visible = !MASK || (j <= pos[h] && j >= lo[h]);
+        const bool visible = !MASK || (j <= pos[h] && (j >= lo[h] || j < keep));
         const float v = visible ? s[nt][2 * h + e] * scale_log2 : -INFINITY;
         s[nt][2 * h + e] = v;
         mx = fmaxf(mx, v);
@@ -267,7 +271,12 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
   const int j_hi = min(kv_len, pos0 + nq);
   const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int first_tile = j_lo / BN, end_tile = (j_hi + BN - 1) / BN;
-  load_kv_tile<BN, PRE_THREADS>(Ks, Vs, p, bt, kvh, first_tile * BN, j_lo, j_hi);
+  // the walk: the tiles of the kept first keys that lie before the window's first tile, then the window's
+  const int keep = p.window > 0 ? min(p.keep_first, j_hi) : 0;
+  const int kept_tiles = min((keep + BN - 1) / BN, first_tile);
+  const int walk_end = end_tile - first_tile + kept_tiles;
+  auto tile_of = [&](int w) { return w < kept_tiles ? w : first_tile + (w - kept_tiles); };
+  load_kv_tile<BN, PRE_THREADS>(Ks, Vs, p, bt, kvh, tile_of(0) * BN, j_lo, j_hi, keep);
   cp_async_commit();
 
   int pos[2], lo[2];
@@ -295,15 +304,16 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
   uint32_t qf[Q_IN_REGS ? D / 16 : 1][4];
   const char* my_q = Qs + warp * 16 * ROW_BYTES;
 
-  for (int tile = first_tile; tile < end_tile; ++tile) {
-    const int buf = (tile - first_tile) & 1;
-    if (tile + 1 < end_tile)
+  for (int walk = 0; walk < walk_end; ++walk) {
+    const int tile = tile_of(walk);
+    const int buf = walk & 1;
+    if (walk + 1 < walk_end)
       load_kv_tile<BN, PRE_THREADS>(Ks + (buf ^ 1) * BN * ROW_BYTES, Vs + (buf ^ 1) * BN * ROW_BYTES, p, bt,
-                                    kvh, (tile + 1) * BN, j_lo, j_hi);
+                                    kvh, tile_of(walk + 1) * BN, j_lo, j_hi, keep);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    if (Q_IN_REGS && tile == first_tile) {
+    if (Q_IN_REGS && walk == 0) {
       const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
       for (int kstep = 0; kstep < D / 16; ++kstep)
@@ -316,10 +326,10 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
       qk_tile<BN / 8>(s, my_q, qf, Ks + buf * BN * ROW_BYTES, 0, lane);
-      if (tile * BN + BN - 1 <= warp_min_pos && tile * BN >= warp_max_lo)
+      if (tile * BN + BN - 1 <= warp_min_pos && (tile * BN >= warp_max_lo || tile * BN + BN <= keep))
         softmax_tile<BN / 8, false>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane);
       else
-        softmax_tile<BN / 8, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane);
+        softmax_tile<BN / 8, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, keep);
       pv_tile<BN / 8>(o, s, Vs + buf * BN * ROW_BYTES, 0, lane);
     }
     __syncthreads();
@@ -333,8 +343,15 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     if (r >= n_valid) continue;
-    const float inv = sum > 0.f ? 1.f / sum : 0.f;
     const int qi = QPT > 1 ? r / GT : 0, gg = QPT > 1 ? r % GT : r;
+    float alpha = 1.f;
+    if (p.sinks) {            // one more term of the sum, in the log2 domain like the running maximum
+      const float sk = p.sinks[kvh * G + g0 + gg] * LOG2E;
+      const float m_new = fmaxf(m[h], sk);
+      alpha = m[h] == -INFINITY ? 0.f : exp2f(m[h] - m_new);
+      sum = sum * alpha + exp2f(sk - m_new);
+    }
+    const float inv = sum > 0.f ? alpha / sum : 0.f;
     bf16* dst = p.out + ((size_t)(q_begin + q0 + qi) * p.H + kvh * G + g0 + gg) * D;
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt)
@@ -499,17 +516,22 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
   const int* bt = p.block_table + (size_t)b * p.max_blocks;
   const int qpos = kv_len - 1;
   const int j_hi = kv_len, j_lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
-  const int first_tile = j_lo / BN, total = (j_hi + BN - 1) / BN - first_tile;
+  // the walk over the key tiles: the tiles of the kept first keys that lie before the window's first
+  // tile, then the window's; the key ranges cut the walk
+  const int keep = p.window > 0 ? min(p.keep_first, j_hi) : 0;
+  const int first_tile = j_lo / BN, kept_tiles = min((keep + BN - 1) / BN, first_tile);
+  const int total = (j_hi + BN - 1) / BN - first_tile + kept_tiles;
+  auto tile_of = [&](int w) { return w < kept_tiles ? w : first_tile + (w - kept_tiles); };
   const int per_split = (total + p.num_splits - 1) / p.num_splits;
-  const int tile_begin = first_tile + split * per_split;
-  const int n_tiles = max(0, min(first_tile + total, tile_begin + per_split) - tile_begin);
+  const int walk_begin = split * per_split;
+  const int n_tiles = max(0, min(total, walk_begin + per_split) - walk_begin);
   const int newest_tile = qpos / BN;
   // from the projection itself the newest key never comes from the cache: every tile may be
   // fetched before the wait, without that key, which this block makes itself
   const bool from_qkv = p.from_qkv != 0;
   const int j_load = from_qkv ? j_hi - 1 : j_hi;
   const int late_tile = from_qkv ? -1 : newest_tile;
-  const bool has_newest = from_qkv && newest_tile >= tile_begin && newest_tile < tile_begin + n_tiles;
+  const bool has_newest = from_qkv && total - 1 >= walk_begin && total - 1 < walk_begin + n_tiles;   // (the walk ends with it)
   __shared__ __align__(16) bf16 newest_kv[2 * D];
 
   // tile `tile` of the keys and values into stage `stage`
@@ -533,12 +555,12 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
         }
       }
     } else {
-      load_kv_tile<BN, THREADS>(Ks + stage * KV_TILE, Vs + stage * KV_TILE, p, bt, kvh, tile * BN, j_lo, j_end);
+      load_kv_tile<BN, THREADS>(Ks + stage * KV_TILE, Vs + stage * KV_TILE, p, bt, kvh, tile * BN, j_lo, j_end, keep);
     }
   };
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s)
-    if (s < n_tiles && tile_begin + s != late_tile) load_tile(s, tile_begin + s, j_load);
+    if (s < n_tiles && tile_of(walk_begin + s) != late_tile) load_tile(s, tile_of(walk_begin + s), j_load);
   // the timeline build follows the blocks of one (request, KV group): marks 40.. with the key
   // range as their value
   const bool traced = blockIdx.x == 0 && blockIdx.z == 0 && threadIdx.x == 0;
@@ -592,7 +614,7 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
   }
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_tiles && tile_begin + s == late_tile) load_tile(s, tile_begin + s, j_hi);
+    if (s < n_tiles && tile_of(walk_begin + s) == late_tile) load_tile(s, tile_of(walk_begin + s), j_hi);
     // the first group holds the query and all of these tiles; the others stay empty, so that the
     // loop below finds as many groups as it counts on
     cp_async_commit();
@@ -617,7 +639,7 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
 
   for (int it = 0; it < n_tiles; ++it) {
     const int nxt = it + DEC_STAGES - 1;
-    if (nxt < n_tiles) load_tile(nxt % DEC_STAGES, tile_begin + nxt, j_load);
+    if (nxt < n_tiles) load_tile(nxt % DEC_STAGES, tile_of(walk_begin + nxt), j_load);
     if (TMA) {
       // bounded; a wait that ran out raises the block's abort flag and the status word, the loop
       // goes on over whatever the stage holds, and the block stores no output at the end
@@ -627,7 +649,7 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
       cp_async_wait<DEC_STAGES - 1>();
     }
     __syncthreads();
-    if (has_newest && tile_begin + it == newest_tile) {
+    if (has_newest && tile_of(walk_begin + it) == newest_tile) {
       // the newest key and value take their row of the tile (the copy left zeros or stale bytes there)
       const int row = qpos - newest_tile * BN, buf_n = it % DEC_STAGES;
       for (int d = threadIdx.x * 2; d < 2 * D; d += THREADS * 2) {
@@ -646,11 +668,11 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
         ldmatrix_x4(qf[kstep], smem_u32(Qs + ((mi & 1) * 8 + r) * ROW_BYTES + (kstep * 2 + (mi >> 1)) * 16));
     }
     const int buf = it % DEC_STAGES;
-    const int jbase = (tile_begin + it) * BN + warp * 16;
+    const int jbase = tile_of(walk_begin + it) * BN + warp * 16;
     if (jbase < j_hi) {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       qk_tile<2, TMA>(s, Qs, qf, Ks + buf * KV_TILE, warp * 16, lane);
-      softmax_tile<2>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane);
+      softmax_tile<2>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane, keep);
       pv_tile<2, TMA>(o, s, Vs + buf * KV_TILE, warp * 16, lane);
     }
     __syncthreads();
@@ -695,6 +717,15 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
       den = fmaf(wgt, sm_ml[(w * 16 + r) * 2 + 1], den);
     }
     const int head = kvh * G + g0 + r;
+    if (p.sinks && split == 0) {
+      // the sink joins the first key range's partial sum (log2 domain, like the maxima)
+      const float sk = p.sinks[head] * LOG2E;
+      const float m_new = fmaxf(mx, sk);
+      const float a = mx == -INFINITY ? 0.f : exp2f(mx - m_new);
+      num *= a;
+      den = den * a + exp2f(sk - m_new);
+      mx = m_new;
+    }
     if (p.num_splits == 1) {
       if (stores) p.out[((size_t)q_begin * p.H + head) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     } else if (p.cluster_merge) {
@@ -826,8 +857,13 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
                                      int page_size, int max_blocks, float scale, int window,
                                      int num_splits, float* part_o, float* part_ml,
                                      int decode_only, const int* tile_req, const int* tile_q0, int num_tiles,
-                                     int tile_queries, int num_pages, cudaStream_t stream) {
-  return paged_attention_mma_impl(nullptr, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
+                                     int tile_queries, int num_pages, int keep_first, const float* sinks,
+                                     cudaStream_t stream) {
+  TS_REQUIRE(keep_first >= 0, "paged_attention_mma: keep_first %d", keep_first);
+  MmaAttnParams extra = {};
+  extra.keep_first = keep_first;
+  extra.sinks = sinks;
+  return paged_attention_mma_impl(&extra, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits,
                                   part_o, part_ml, decode_only, tile_req, tile_q0, num_tiles,
                                   tile_queries, num_pages, stream);

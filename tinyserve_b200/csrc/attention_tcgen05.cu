@@ -72,6 +72,8 @@ struct TcAttnParams {
   int H, Hkv, page_shift, page_size, max_blocks;
   int heads_per_tile, queries_per_tile, head_tiles;     // of one query tile
   int window;
+  int keep_first;           // with a window: keys below this stay visible (their tiles come first in the walk)
+  const float* sinks;       // [H] or null: one more term exp(sinks[h]) in every softmax sum of head h
   float scale_log2;
 };
 
@@ -162,7 +164,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int j_hi = min(kv_len, pos0 + nq_all);
   const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int first_tile = j_lo / BN, end_tile = (j_hi + BN - 1) / BN;
-  const int n_tiles = nq_all > 0 ? end_tile - first_tile : 0;
+  // the walk over the key tiles: those of the kept first keys that lie before the window's first tile, then the window's
+  const int keep = p.window > 0 ? min(p.keep_first, j_hi) : 0;
+  const int kept_tiles = min((keep + BN - 1) / BN, first_tile);
+  const int n_tiles = nq_all > 0 ? end_tile - first_tile + kept_tiles : 0;
+  auto tile_of = [&](int t) { return t < kept_tiles ? t : first_tile + (t - kept_tiles); };
   // the timeline build follows one block through its tiles (marks 10.. by the issuer, 20.. by a
   // softmax thread of each query tile, 30 by the loader; the value is the key tile)
   const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
@@ -187,7 +193,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // stage cannot complete before it.
       auto load = [&](bool keys, int t) -> bool {
         const int stages = keys ? K_STAGES : V_STAGES, s = t % stages;
-        const int j0 = (first_tile + t) * BN;
+        const int j0 = tile_of(t) * BN;
         int ok = 1;
         if (lane == 0)
           ok = mbar_wait(smem_u32(keys ? &k_empty[s] : &v_empty[s]), ((t / stages) & 1) ^ 1, abort_flag) ? 1 : 0;
@@ -318,13 +324,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) mbar_arrive(smem_u32(&o_zeroed[g]));
       }
       for (int t = 0; t < n_tiles; ++t) {
-        const int j0 = (first_tile + t) * BN;
+        const int j0 = tile_of(t) * BN;
         ok = mbar_wait(smem_u32(&s_full[g]), t & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
         if (tracer) timeline_mark_thread(20 + 4 * g, t);
-        const bool all_visible = j0 + BN - 1 <= pos && j0 >= lo;
+        const bool all_visible = j0 + BN - 1 <= pos && (j0 >= lo || j0 + BN <= keep);
         // the whole row of S into registers: four loads in flight, one wait
         float sv[BN];
 #pragma unroll
@@ -335,7 +341,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int e = 0; e < BN; ++e) {
             const int j = j0 + e;
-            if (!(j <= pos && j >= lo)) sv[e] = -INFINITY;
+            if (!(j <= pos && (j >= lo || j < keep))) sv[e] = -INFINITY;
           }
         }
         // the row's maximum, four independent chains
@@ -403,7 +409,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       if (ok) {
         tcgen05_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        float alpha = 1.f;
+        if (p.sinks && valid) {       // (log2 domain, like the running maximum; O is scaled on its way out)
+          const float sk = p.sinks[kvh * G + g0 + gg] * 1.4426950408889634f;
+          const float m_new = fmaxf(m, sk);
+          alpha = m == -INFINITY ? 0.f : exp2f(m - m_new);
+          l = l * alpha + exp2f(sk - m_new);
+        }
+        const float inv = l > 0.f ? alpha / l : 0.f;
         bf16* dst = p.out + ((size_t)(q_begin + qg + qi) * p.H + kvh * G + g0 + gg) * D;
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
@@ -465,7 +478,8 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
                                          int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
                                          int num_pages, int page_size, int max_blocks, float scale, int window,
                                          const int* tile_req, const int* tile_q0, int num_tiles,
-                                         int tile_queries, cudaStream_t stream) {
+                                         int tile_queries, int keep_first, const float* sinks, cudaStream_t stream) {
+  TS_REQUIRE(keep_first >= 0, "paged_attention_tcgen05: keep_first %d", keep_first);
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_tcgen05: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_tcgen05: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size >= 8 && page_size <= BN && (page_size & (page_size - 1)) == 0,
@@ -478,6 +492,7 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
   p.out = (bf16*)out; p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens;
   p.tile_req = tile_req; p.tile_q0 = tile_q0;
   p.H = H; p.Hkv = Hkv; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;
+  p.keep_first = keep_first; p.sinks = sinks;
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -13,6 +13,9 @@
 //  * ts_moe_route: softmax over all experts of a token's router logits; the `top` largest keep
 //    their probability (not renormalised), the others get zero.
 //  * ts_moe_activate: a[t, e, :] <- act(a[t, e, :]) * gate[t, e], act = relu squared.
+//  * ts_moe_group, ts_moe_gather, ts_moe_combine: the tokens of a step sorted by expert (every
+//    expert's rows a run that starts at a multiple of 16), their inputs gathered into that order,
+//    and the experts' outputs added back per token with the router's weights in 32-bit.
 //  * ts_batched_matmul: C[b] = A[b] B[b] with 32-bit FMA (any strides), chains of 64 k.
 #include "common.cuh"
 
@@ -189,9 +192,76 @@ __global__ void moe_activate_kernel(T* __restrict__ a, const float* __restrict__
   const size_t t = blockIdx.x;
   T* row = a + t * (size_t)E * ff;
   for (int i = threadIdx.x; i < E * ff; i += blockDim.x) {
-    const float g = gates[t * E + i / ff];
+    const float g = gates ? gates[t * E + i / ff] : 1.f;
     const float v = fmaxf(to_f32<T>(row[i]), 0.f);
     row[i] = from_f32<T>(g == 0.f ? 0.f : v * v * g);
+  }
+}
+
+// Rows by expert.  One block: counts per expert, the runs' starts (each a multiple of ALIGN rows),
+// then a row for every (token, expert) pair with a gate above zero.  Within a run the rows are in
+// the order the threads arrive; a row's result does not depend on its place.
+constexpr int GROUP_ALIGN = 16;
+__global__ void __launch_bounds__(1024) moe_group_kernel(const float* __restrict__ gates, int num_tokens, int E,
+                                                         int* __restrict__ row_token, int* __restrict__ pair_row,
+                                                         int* __restrict__ ends, int capacity) {
+  extern __shared__ int sh[];          // [E] counts, then cursors
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) sh[e] = 0;
+  for (int i = threadIdx.x; i < capacity; i += blockDim.x) row_token[i] = -1;
+  __syncthreads();
+  const int pairs = num_tokens * E;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+    if (gates[i] > 0.f) atomicAdd(&sh[i % E], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      const int n = sh[e];
+      sh[e] = at;                                        // the run's cursor
+      at += (n + GROUP_ALIGN - 1) / GROUP_ALIGN * GROUP_ALIGN;
+      ends[e] = at;                                      // the run ends where the next one starts (padding rows are zeros)
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    int row = -1;
+    if (gates[i] > 0.f) {
+      row = atomicAdd(&sh[i % E], 1);
+      row_token[row] = i / E;
+    }
+    pair_row[i] = row;
+  }
+}
+
+// x_sorted[row] = x[row_token[row]] (zeros where the row is padding)
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ row_token, T* __restrict__ out, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const int t = row_token[row];
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(t < 0 ? 0 : t) * n);
+  uint4* dst = reinterpret_cast<uint4*>(out + row * n);
+  const int chunks = n * (int)sizeof(T) / 16;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = t < 0 ? make_uint4(0u, 0u, 0u, 0u) : src[c];
+}
+
+// out[t] = sum_e gates[t, e] * y[pair_row[t, e]] over the experts the token chose, in expert order
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ gates, const int* __restrict__ pair_row,
+                                   T* __restrict__ out, int E, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float acc = 0.f;
+    for (int e = 0; e < E; ++e) {
+      const int row = pair_row[t * E + e];
+      if (row >= 0) acc = fmaf(gates[t * E + e], to_f32<T>(y[(size_t)row * n + c]), acc);
+    }
+    out[t * n + c] = from_f32<T>(acc);
   }
 }
 
@@ -327,10 +397,46 @@ TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, in
 }
 
 TS_EXPORT int ts_moe_activate(int dtype, void* a, const float* gates, int num_tokens, int E, int ff, cudaStream_t stream) {
-  TS_REQUIRE(num_tokens > 0 && E > 0 && ff > 0 && a && gates, "moe_activate: empty input");
+  TS_REQUIRE(num_tokens > 0 && E > 0 && ff > 0 && a, "moe_activate: empty input");      // (gates null: the plain activation)
   if (dtype == TS_F32) TS_LAUNCH("moe_activate", moe_activate_kernel<float>, num_tokens, 256, 0, stream, (float*)a, gates, E, ff);
   else if (dtype == TS_BF16) TS_LAUNCH("moe_activate", moe_activate_kernel<__nv_bfloat16>, num_tokens, 256, 0, stream, (__nv_bfloat16*)a, gates, E, ff);
   else return ts_fail("moe_activate: unknown dtype %d", dtype);
+  return 0;
+}
+
+TS_EXPORT int ts_moe_group_align() { return GROUP_ALIGN; }
+
+// row_token [capacity] (capacity >= tokens * top + E * (align - 1)), pair_row [tokens, E], ends [E]
+TS_EXPORT int ts_moe_group(const float* gates, int num_tokens, int E, int* row_token, int* pair_row, int* ends, int capacity,
+                           cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && E > 0 && E <= 4096 && gates && row_token && pair_row && ends && capacity > 0, "moe_group: empty input");
+  TS_LAUNCH("moe_group", moe_group_kernel, 1, 1024, (size_t)E * sizeof(int), stream, gates, num_tokens, E, row_token, pair_row, ends,
+            capacity);
+  return 0;
+}
+
+TS_EXPORT int ts_moe_gather(int dtype, const void* x, const int* row_token, void* out, int rows, int n, cudaStream_t stream) {
+  TS_REQUIRE(rows > 0 && n > 0 && x && row_token && out, "moe_gather: empty input");
+  TS_REQUIRE(((uintptr_t)x | (uintptr_t)out) % 16 == 0, "moe_gather: operands must be 16-byte aligned");
+  if (dtype == TS_F32) {
+    TS_REQUIRE(n % 4 == 0, "moe_gather: rows of %d floats are no multiple of 16 bytes", n);
+    TS_LAUNCH("moe_gather", moe_gather_kernel<float>, rows, 128, 0, stream, (const float*)x, row_token, (float*)out, n);
+  } else if (dtype == TS_BF16) {
+    TS_REQUIRE(n % 8 == 0, "moe_gather: rows of %d bfloat16 are no multiple of 16 bytes", n);
+    TS_LAUNCH("moe_gather", moe_gather_kernel<__nv_bfloat16>, rows, 128, 0, stream, (const __nv_bfloat16*)x, row_token, (__nv_bfloat16*)out, n);
+  } else {
+    return ts_fail("moe_gather: unknown dtype %d", dtype);
+  }
+  return 0;
+}
+
+TS_EXPORT int ts_moe_combine(int dtype, const void* y, const float* gates, const int* pair_row, void* out, int num_tokens, int E,
+                             int n, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && E > 0 && n > 0 && y && gates && pair_row && out, "moe_combine: empty input");
+  const int threads = n >= 1024 ? 256 : 128;
+  if (dtype == TS_F32) TS_LAUNCH("moe_combine", moe_combine_kernel<float>, num_tokens, threads, 0, stream, (const float*)y, gates, pair_row, (float*)out, E, n);
+  else if (dtype == TS_BF16) TS_LAUNCH("moe_combine", moe_combine_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)y, gates, pair_row, (__nv_bfloat16*)out, E, n);
+  else return ts_fail("moe_combine: unknown dtype %d", dtype);
   return 0;
 }
 

@@ -803,7 +803,7 @@ def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
     return max(1, min(2 * num_sms() // blocks, max_kv_len // 128, 32))
 
 
-def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
+def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first=0, sinks=None):
     """The one-token requests of a mixed batch, by the tensor-core decode kernel."""
     T, H, D = q.shape
     Hkv = k_cache.shape[1]
@@ -820,7 +820,8 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
         _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(1), c_int(H), c_int(Hkv),
         c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale), c_int(window),
         c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(2 if cluster else 1), _ptr(work.dec_req),
-        _ptr(work.dec_tok), c_int(n), c_int(0), c_int(_tma_pages(k_cache, v_cache)), _stream()),
+        _ptr(work.dec_tok), c_int(n), c_int(0), c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks),
+        _stream()),
         2 if num_splits > 1 and not cluster else 1)
 
 
@@ -833,12 +834,6 @@ def attention_backend(dtype, head_dim, page_size=16) -> str:
     if head_dim in TCGEN05_HEAD_DIMS and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0:
         return "tcgen05"
     return "mma"
-
-
-def attention_backend_with(chosen: str, keep_first: int, has_sinks: bool) -> str:
-    """The kernels that attend when the first keys of a sequence stay visible beside a window, or a
-    sink joins the softmax sum: the 32-bit kernel has both."""
-    return "simt" if (keep_first or has_sinks) else chosen
 
 
 def prefill_tile_queries(dtype, num_heads, num_kv_heads, head_dim, page_size=16) -> int:
@@ -870,8 +865,6 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (H,) or not sinks.is_cuda):
         raise TypeError("paged_attention: sinks are float32 [heads] on the device")
     keep_first = int(keep_first) if window > 0 else 0
-    if (keep_first or sinks is not None) and backend is None:
-        backend = attention_backend_with(chosen, keep_first, sinks is not None)
     if backend is not None and backend != chosen:
         if q.dtype != torch.bfloat16 or (backend == "tcgen05") or (backend == "mma" and chosen == "simt"):
             raise ValueError(f"attention backend {backend!r} does not take {q.dtype}, head size {D}, pages of {page}")
@@ -886,14 +879,14 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         tile_queries = prefill_tile_queries(q.dtype, H, Hkv, D, page)
         work = attention_work(ctx, tile_queries, q.device)
         if work.num_decode:
-            _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work)
+            _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks)
         if work.num_tiles:
             _check(lib, lib.ts_paged_attention_tcgen05(
                 _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
                 _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H), c_int(Hkv),
                 c_int(k_cache.shape[0]), c_int(page), c_int(view.block_table.stride(0)), c_float(scale),
                 c_int(window), _ptr(work.tile_req), _ptr(work.tile_q0), c_int(work.num_tiles),
-                c_int(tile_queries), _stream()))
+                c_int(tile_queries), c_int(keep_first), _ptr(sinks), _stream()))
         return out
     if num_splits is None:
         if decode:
@@ -920,7 +913,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             tile_queries = MMA_PREFILL_ROWS // group if group < MMA_PREFILL_ROWS else 1
             work = attention_work(ctx, tile_queries, q.device)
             if work.num_decode:
-                _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work)
+                _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks)
             if not work.num_tiles:
                 return out
             tile_req, tile_q0, num_tiles = work.tile_req, work.tile_q0, work.num_tiles
@@ -930,7 +923,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
             c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml),
             c_int((2 if cluster else 1) if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
-            c_int(_tma_pages(k_cache, v_cache)), _stream()), launches)
+            c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks), _stream()), launches)
         return out
     lib = _attention(D)
     _check(lib, lib.ts_paged_attention(
@@ -1472,3 +1465,38 @@ def moe_activate_(a, gates, num_experts):
     _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), _ptr(gates), c_int(T), c_int(num_experts),
                                     c_int(a.shape[1] // num_experts), _stream()))
     return a
+
+
+#: from this many tokens on (bfloat16, fewer experts chosen than there are) a step's tokens are sorted by
+#: expert and every expert multiplies its own rows only; below, all experts run on all tokens and the
+#: unchosen ones are multiplied by zero (a few decoded tokens touch most experts' weights anyway, and the
+#: dense products are this package's tcgen05 kernels)
+MOE_GROUPED_MIN_TOKENS = 256
+
+
+def moe_grouped(h, gates, up, down_side_by_side, top):
+    """Mixture of experts over rows sorted by expert.  h [T, n] bfloat16; gates float32 [T, E] (zero:
+    not chosen); up [E ff, n] (expert by expert); down_side_by_side [n, E ff].  Returns [T, n]:
+    sum over a token's experts of gate * W_down,e relu(W_up,e h)^2, the sum in 32-bit.  The two
+    products over ragged row groups are the library's grouped product."""
+    _cuda(h, gates, up, down_side_by_side)
+    T, n = h.shape
+    E = gates.shape[1]
+    ff = up.shape[0] // E
+    lib = _latent_moe()
+    align = lib.ts_moe_group_align()
+    capacity = -(-(T * top + E * (align - 1)) // align) * align + align
+    meta = torch.empty(capacity + T * E + E, dtype=torch.int32, device=h.device)
+    row_token, pair_row, ends = meta[:capacity], meta[capacity:capacity + T * E], meta[capacity + T * E:]
+    _check(lib, lib.ts_moe_group(_ptr(gates), c_int(T), c_int(E), _ptr(row_token), _ptr(pair_row), _ptr(ends), c_int(capacity),
+                                 _stream()))
+    x = torch.empty(capacity, n, dtype=h.dtype, device=h.device)
+    _check(lib, lib.ts_moe_gather(c_int(_dt(h)), _ptr(h), _ptr(row_token), _ptr(x), c_int(capacity), c_int(n), _stream()))
+    a = torch.nn.functional.grouped_mm(x, up.view(E, ff, n).transpose(1, 2), offs=ends)
+    _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), None, c_int(capacity), c_int(1), c_int(ff), _stream()))
+    y = torch.nn.functional.grouped_mm(a, down_side_by_side.view(n, E, ff).permute(1, 2, 0), offs=ends)
+    out = torch.empty(T, n, dtype=h.dtype, device=h.device)
+    _check(lib, lib.ts_moe_combine(c_int(_dt(y)), _ptr(y), _ptr(gates), _ptr(pair_row), _ptr(out), c_int(T), c_int(E), c_int(n),
+                                   _stream()))
+    count_launches(2)
+    return out

@@ -99,9 +99,6 @@ class Attention(Mixer):
     accepts_scaled_rows = True
 
     def work_tile_queries(self, dtype, page_size):
-        backend = ops.attention_backend(dtype, self.stored_dim, page_size)
-        if ops.attention_backend_with(backend, self.keep_first, False) == "simt":
-            return 0
         return ops.prefill_tile_queries(dtype, self.num_heads, self.num_kv_heads, self.stored_dim, page_size)
 
     def _forward_general(self, h, ctx, call):

@@ -92,6 +92,9 @@ class LatentAttention(Mixer):
 
     accepts_scaled_rows = True
 
+    def work_tile_queries(self, dtype, page_size):
+        return ops.prefill_tile_queries(dtype, self.num_heads, 1, self.stored_dim, page_size)
+
     def forward(self, h, ctx, call):
         H, n, nr, nv, r = self.num_heads, self.head_dim, self.rot_dim, self.value_dim, self.kv_rank
         proj = ops.materialize(ops.linear(h, self.w["in_proj.weight"]))

@@ -7,7 +7,9 @@ W_down,e act(W_up,e h), no biases; the token's output is the weighted sum over i
 The experts' up-projections are stacked into one matrix [E ff, hidden] and their down-projections
 side by side into one [hidden, E ff]: act(.) of an expert that a token did not choose is multiplied
 by zero, the others by their weight, and one product over K = E ff adds the chosen experts'
-outputs in 32-bit inside the product."""
+outputs in 32-bit inside the product.  That is how a few tokens run (decoding: they touch most
+experts' weights anyway) and how the 32-bit engine runs; a bfloat16 step of many tokens sorts its
+rows by expert instead, so that an expert multiplies its own rows only (``ops.moe_grouped``)."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -54,6 +56,9 @@ class MixtureOfExperts(FeedForward):
     def forward(self, h, ctx):
         logits = ops.linear(h, self.w["router.weight"], out_float32=True)
         gates = ops.moe_route(logits, self.top)
+        if (h.dtype == ops.torch.bfloat16 and self.top < self.num_experts and h.shape[0] >= ops.MOE_GROUPED_MIN_TOKENS
+                and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0):
+            return ops.moe_grouped(h, gates, self.w["up.weight"], self.w["down.weight"], self.top)
         a = ops.materialize(ops.linear(h, self.w["up.weight"]))
         ops.moe_activate_(a, gates, self.num_experts)
         return ops.linear(a, self.w["down.weight"], allow_pending=True)
