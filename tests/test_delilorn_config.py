@@ -98,6 +98,15 @@ def test_loader_lists_what_does_not_fit(tmp_path):
         check_checkpoint(build_model(delilorn_config("P")), index, dup)
     assert err.value.missing == ["l1.mix.dkv"] and err.value.unexpected == ["l3.mix.dkv"]
     assert [w[0] for w in err.value.wrong_shape] == ["l1.mlp.e2.up"]
+    # the norms around a feed-forward that layer 2 does not have may be there; nobody reads them
+    weights = load_file(f"{make_delilorn_dir(tmp_path / 'b', 'P', seed=4)}/model.safetensors")
+    weights["l2.norm2"], weights["l2.norm2b"] = weights["l0.norm2"].clone(), weights["l0.norm2"].clone()
+    weights["l1.norm3"] = weights["l0.norm2"].clone()
+    save_file(weights, f"{tmp_path / 'b'}/model.safetensors")
+    index, dup = _index_folder(str(tmp_path / "b"))
+    with pytest.raises(WeightError) as err:
+        check_checkpoint(build_model(delilorn_config("P")), index, dup)
+    assert err.value.unexpected == ["l1.norm3"] and not err.value.missing
 
 
 @pytest.mark.parametrize("rot", [

@@ -173,7 +173,9 @@ class DelilornConfig(ModelConfig):
             source = layer["mixer"].get("kv_from") if layer["type"] == "latent_attention" else None
             entry_of[i] = entry_of[source] if source is not None else i
             order.append(LayerCall(i, entry_of[i], writes_cache=source is None))
+        # a layer without a feed-forward has no use for the two norms around one, should a checkpoint hold them
+        unread = tuple(rf"l{i}\.norm2b?" for i, layer in enumerate(self.layers) if layer.get("mlp") is None)
         return ModelSpec(
             self.vocab, self.width, tuple(layers), tuple(order), norm, tie_word_embeddings=True, weight_prefix="",
             names={"embed": "embed", "layers": "l{i}", "final_norm": "final.norm"},
-            name_rules=((r"\.weight$", ""),))
+            name_rules=((r"\.weight$", ""),), unread_names=unread)

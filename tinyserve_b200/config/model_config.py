@@ -102,6 +102,9 @@ class ModelSpec:
     # checkpoint tensor name the parts ask for: a checkpoint that stores "x.q" where the parts say
     # "x.q.weight" gives ((r"\.weight$", ""),)
     name_rules: tuple = ()
+    # regular expressions of checkpoint tensor names that no part reads and that may be there all
+    # the same (the norms of a sub-layer that a layer does not have, say): they are not "unexpected"
+    unread_names: tuple = ()
 
     def name_of(self, key: str, **fmt) -> str:
         return self.names.get(key, MODEL_NAMES[key]).format(prefix=self.weight_prefix, **fmt)

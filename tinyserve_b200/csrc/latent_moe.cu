@@ -184,17 +184,51 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, float* __rest
     if (g[e] < 0.f) g[e] = 0.f;
 }
 
-// a[t, e * ff + j] <- relu(a)^2 * gates[t, e]
+// 16 bytes of a row as floats and back
+template <typename T> struct Chunk { static constexpr int N = 16 / sizeof(T); };
 template <typename T>
+__device__ __forceinline__ void chunk_load(const T* p, float (&v)[Chunk<T>::N]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Chunk<T>::N; ++i) v[i] = to_f32<T>(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ void chunk_store(T* p, const float (&v)[Chunk<T>::N]) {
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Chunk<T>::N; ++i) e[i] = from_f32<T>(v[i]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// a[t, e * ff + j] <- relu(a)^2 * gates[t, e]; VEC: 16 bytes a thread (ff a multiple of the chunk)
+template <typename T, bool VEC>
 __global__ void moe_activate_kernel(T* __restrict__ a, const float* __restrict__ gates, int E, int ff) {
   pdl_trigger();
   pdl_wait();
   const size_t t = blockIdx.x;
   T* row = a + t * (size_t)E * ff;
-  for (int i = threadIdx.x; i < E * ff; i += blockDim.x) {
-    const float g = gates ? gates[t * E + i / ff] : 1.f;
-    const float v = fmaxf(to_f32<T>(row[i]), 0.f);
-    row[i] = from_f32<T>(g == 0.f ? 0.f : v * v * g);
+  if constexpr (VEC) {
+    constexpr int N = Chunk<T>::N;
+    const int per_expert = ff / N;
+    for (int c = threadIdx.x; c < E * per_expert; c += blockDim.x) {
+      const float g = gates ? gates[t * E + c / per_expert] : 1.f;
+      float v[N];
+      chunk_load<T>(row + (size_t)c * N, v);
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const float r = fmaxf(v[i], 0.f);
+        v[i] = g == 0.f ? 0.f : r * r * g;
+      }
+      chunk_store<T>(row + (size_t)c * N, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < E * ff; i += blockDim.x) {
+      const float g = gates ? gates[t * E + i / ff] : 1.f;
+      const float v = fmaxf(to_f32<T>(row[i]), 0.f);
+      row[i] = from_f32<T>(g == 0.f ? 0.f : v * v * g);
+    }
   }
 }
 
@@ -249,19 +283,48 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
 }
 
 // out[t] = sum_e gates[t, e] * y[pair_row[t, e]] over the experts the token chose, in expert order
-template <typename T>
+template <typename T, bool VEC>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ gates, const int* __restrict__ pair_row,
                                    T* __restrict__ out, int E, int n) {
   pdl_trigger();
   pdl_wait();
   const size_t t = blockIdx.x;
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
-    float acc = 0.f;
-    for (int e = 0; e < E; ++e) {
-      const int row = pair_row[t * E + e];
-      if (row >= 0) acc = fmaf(gates[t * E + e], to_f32<T>(y[(size_t)row * n + c]), acc);
+  if constexpr (VEC) {
+    // the token's experts first (in expert order), then 16 bytes of every chosen row a thread
+    constexpr int N = Chunk<T>::N, MOST = 32;
+    __shared__ int rows[MOST];
+    __shared__ float weights[MOST];
+    __shared__ int count;
+    if (threadIdx.x == 0) {
+      int k = 0;
+      for (int e = 0; e < E && k < MOST; ++e) {
+        const int row = pair_row[t * E + e];
+        if (row >= 0) { rows[k] = row; weights[k] = gates[t * E + e]; ++k; }
+      }
+      count = k;
     }
-    out[t * n + c] = from_f32<T>(acc);
+    __syncthreads();
+    for (int c = threadIdx.x; c < n / N; c += blockDim.x) {
+      float acc[N];
+#pragma unroll
+      for (int i = 0; i < N; ++i) acc[i] = 0.f;
+      for (int k = 0; k < count; ++k) {
+        float v[N];
+        chunk_load<T>(y + (size_t)rows[k] * n + (size_t)c * N, v);
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = fmaf(weights[k], v[i], acc[i]);
+      }
+      chunk_store<T>(out + t * n + (size_t)c * N, acc);
+    }
+  } else {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      float acc = 0.f;
+      for (int e = 0; e < E; ++e) {
+        const int row = pair_row[t * E + e];
+        if (row >= 0) acc = fmaf(gates[t * E + e], to_f32<T>(y[(size_t)row * n + c]), acc);
+      }
+      out[t * n + c] = from_f32<T>(acc);
+    }
   }
 }
 
@@ -398,9 +461,16 @@ TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, in
 
 TS_EXPORT int ts_moe_activate(int dtype, void* a, const float* gates, int num_tokens, int E, int ff, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && E > 0 && ff > 0 && a, "moe_activate: empty input");      // (gates null: the plain activation)
-  if (dtype == TS_F32) TS_LAUNCH("moe_activate", moe_activate_kernel<float>, num_tokens, 256, 0, stream, (float*)a, gates, E, ff);
-  else if (dtype == TS_BF16) TS_LAUNCH("moe_activate", moe_activate_kernel<__nv_bfloat16>, num_tokens, 256, 0, stream, (__nv_bfloat16*)a, gates, E, ff);
-  else return ts_fail("moe_activate: unknown dtype %d", dtype);
+  const bool vec = (uintptr_t)a % 16 == 0 && ff % (dtype == TS_F32 ? 4 : 8) == 0;
+  if (dtype == TS_F32) {
+    if (vec) TS_LAUNCH("moe_activate", (moe_activate_kernel<float, true>), num_tokens, 256, 0, stream, (float*)a, gates, E, ff);
+    else TS_LAUNCH("moe_activate", (moe_activate_kernel<float, false>), num_tokens, 256, 0, stream, (float*)a, gates, E, ff);
+  } else if (dtype == TS_BF16) {
+    if (vec) TS_LAUNCH("moe_activate", (moe_activate_kernel<__nv_bfloat16, true>), num_tokens, 256, 0, stream, (__nv_bfloat16*)a, gates, E, ff);
+    else TS_LAUNCH("moe_activate", (moe_activate_kernel<__nv_bfloat16, false>), num_tokens, 256, 0, stream, (__nv_bfloat16*)a, gates, E, ff);
+  } else {
+    return ts_fail("moe_activate: unknown dtype %d", dtype);
+  }
   return 0;
 }
 
@@ -433,10 +503,18 @@ TS_EXPORT int ts_moe_gather(int dtype, const void* x, const int* row_token, void
 TS_EXPORT int ts_moe_combine(int dtype, const void* y, const float* gates, const int* pair_row, void* out, int num_tokens, int E,
                              int n, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && E > 0 && n > 0 && y && gates && pair_row && out, "moe_combine: empty input");
-  const int threads = n >= 1024 ? 256 : 128;
-  if (dtype == TS_F32) TS_LAUNCH("moe_combine", moe_combine_kernel<float>, num_tokens, threads, 0, stream, (const float*)y, gates, pair_row, (float*)out, E, n);
-  else if (dtype == TS_BF16) TS_LAUNCH("moe_combine", moe_combine_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)y, gates, pair_row, (__nv_bfloat16*)out, E, n);
-  else return ts_fail("moe_combine: unknown dtype %d", dtype);
+  const int threads = n >= 2048 ? 256 : 128;
+  // (a token of more than 32 experts takes the plain form)
+  const bool vec = ((uintptr_t)y | (uintptr_t)out) % 16 == 0 && n % (dtype == TS_F32 ? 4 : 8) == 0 && E <= 32;
+  if (dtype == TS_F32) {
+    if (vec) TS_LAUNCH("moe_combine", (moe_combine_kernel<float, true>), num_tokens, threads, 0, stream, (const float*)y, gates, pair_row, (float*)out, E, n);
+    else TS_LAUNCH("moe_combine", (moe_combine_kernel<float, false>), num_tokens, threads, 0, stream, (const float*)y, gates, pair_row, (float*)out, E, n);
+  } else if (dtype == TS_BF16) {
+    if (vec) TS_LAUNCH("moe_combine", (moe_combine_kernel<__nv_bfloat16, true>), num_tokens, threads, 0, stream, (const __nv_bfloat16*)y, gates, pair_row, (__nv_bfloat16*)out, E, n);
+    else TS_LAUNCH("moe_combine", (moe_combine_kernel<__nv_bfloat16, false>), num_tokens, threads, 0, stream, (const __nv_bfloat16*)y, gates, pair_row, (__nv_bfloat16*)out, E, n);
+  } else {
+    return ts_fail("moe_combine: unknown dtype %d", dtype);
+  }
   return 0;
 }
 

@@ -27,6 +27,20 @@ TCGEN05_MAX_TOKENS = 64
 TCGEN05_HEAD_DIMS = (64, 128)
 MMA_MAX_HEAD_DIM = 256
 MMA_PREFILL_ROWS = 64           # query rows of a block of the mma prefill kernel (4 warps of 16)
+#: heads wider than this run the mma prefill kernel with 8 warps (128 rows a block): a block of such
+#: heads holds one key tile pair per SM anyway, and twice the rows share its loads and hide its waits
+MMA_WIDE_HEAD = 128
+
+
+def mma_prefill_rows(head_dim: int) -> int:
+    return 2 * MMA_PREFILL_ROWS if head_dim > MMA_WIDE_HEAD else MMA_PREFILL_ROWS
+
+
+def _mma_defines(head_dim: int) -> dict:
+    defines = {"TS_HEAD_DIM": head_dim}
+    if head_dim > MMA_WIDE_HEAD:
+        defines["TS_PREFILL_WARPS"] = 8
+    return defines
 #: the key ranges of a split-KV decode are the blocks of a thread-block cluster and merge through
 #: distributed shared memory when there are at most this many; more are merged by a second kernel
 #: (measured on B200 from CUDA graphs, 8 requests x 640 keys: 14.4 us with the second launch,
@@ -475,7 +489,7 @@ def _attention(head_dim: int):
 
 
 def _attention_mma(head_dim: int):
-    return build.load_unit("attention_mma.cu", {"TS_HEAD_DIM": head_dim})
+    return build.load_unit("attention_mma.cu", _mma_defines(head_dim))
 
 
 def _attention_tcgen05(head_dim: int):
@@ -506,7 +520,7 @@ def units_for(head_dims, key_dims=()) -> list:
     units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("gemm_tcgen05.cu", {}), ("gemm_pair_tcgen05.cu", {}),
              ("sampler.cu", {}), ("latent_moe.cu", {})]
     units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
-    units += [("attention_mma.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
+    units += [("attention_mma.cu", _mma_defines(d)) for d in sorted(set(head_dims))
               if d <= MMA_MAX_HEAD_DIM]
     units += [("attention_tcgen05.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
               if d in TCGEN05_HEAD_DIMS]
@@ -844,7 +858,8 @@ def prefill_tile_queries(dtype, num_heads, num_kv_heads, head_dim, page_size=16)
     if backend == "tcgen05":
         return 2 * (128 // group if group < 128 else 1)      # two query tiles of 128 rows a block
     if backend == "mma":
-        return MMA_PREFILL_ROWS // group if group < MMA_PREFILL_ROWS else 1
+        rows = mma_prefill_rows(head_dim)
+        return rows // group if group < rows else 1
     return 0
 
 
@@ -910,7 +925,8 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         num_tiles = tile_queries = 0
         if not decode:
             group = H // Hkv
-            tile_queries = MMA_PREFILL_ROWS // group if group < MMA_PREFILL_ROWS else 1
+            rows = mma_prefill_rows(D)
+            tile_queries = rows // group if group < rows else 1
             work = attention_work(ctx, tile_queries, q.device)
             if work.num_decode:
                 _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks)

@@ -116,8 +116,10 @@ def check_checkpoint(model, index, duplicates=()):
     names = {e.name for e in expected}
     missing = [e.name for e in expected if e.name not in index]
     tied = model.lm_head is None if hasattr(model, "lm_head") else False
+    unread = [re.compile(pattern) for pattern in getattr(getattr(model, "spec", None), "unread_names", ())]
     unexpected = [k for k in sorted(index) if k not in names
-                  and not (tied and k == "lm_head.weight")]
+                  and not (tied and k == "lm_head.weight")
+                  and not any(pattern.fullmatch(k) for pattern in unread)]
     wrong = [(e.name, index[e.name][1], e.shape) for e in expected
              if e.name in index and tuple(index[e.name][1]) != tuple(e.shape)]
     if missing or unexpected or wrong or duplicates:
