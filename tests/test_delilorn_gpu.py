@@ -169,6 +169,27 @@ def test_attention_with_kept_first_keys_and_sinks(dtype, tol, H, G, D, page, mas
             assert (out.double().cpu() - want).abs().max() <= tol * want.abs().max(), (backend, splits)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-6), (torch.bfloat16, 1.5e-2)])
+@pytest.mark.parametrize("H,G,D,page", [(4, 2, 64, 16), (2, 1, 128, 64), (6, 3, 32, 8)])
+@pytest.mark.parametrize("mask", [{"size": 50, "keep_first": 7}, {"size": 130, "keep_first": 129}, {"size": 200, "keep_first": 140}])
+def test_long_prompt_walks_the_kept_tiles_first(dtype, tol, H, G, D, page, mask):
+    """A prompt of 420 tokens in one portion, and the same prompt's last 150 tokens after a prefix:
+    the window's first tile lies behind the kept keys' tiles in every kernel (key tiles of 32, 64
+    and 128), kept keys fill a tile, end in the middle of one, and reach into the window's first tile."""
+    kv_lens, q_lens = [420, 420], [420, 150]
+    k = [draws(n, G, D, seed=50 + i).to(dtype) for i, n in enumerate(kv_lens)]
+    v = [draws(n, G, D, seed=60 + i).to(dtype) for i, n in enumerate(kv_lens)]
+    q = draws(sum(q_lens), H, D, seed=70).to(dtype)
+    sinks = (draws(H, seed=71, scale=2.0) + 1.0).float()
+    kc, table = _paged(k, page, sum(-(-n // page) for n in kv_lens) + 3, seed=3)
+    vc, _ = _paged(v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=3)
+    scale = 3.0 / math.sqrt(D)
+    want = _attention_plain(q, k, v, q_lens, scale, mask, sinks)
+    for backend in attention_backends(dtype, D, page, mask, sinks):
+        out = _run_attention(q.to(DEV), kc, vc, table, q_lens, kv_lens, page, scale, mask, sinks.to(DEV), None, backend)
+        assert (out.double().cpu() - want).abs().max() <= tol * want.abs().max(), backend
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_sees_exactly_the_window_and_the_kept_keys(dtype):
     """One key stands out (its score is far above all others): the output is its value when it is
