@@ -345,10 +345,13 @@ def test_router_keeps_the_largest_probabilities_as_they_are(E, top):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("E,top,ff,width", [(4, 2, 40, 64), (6, 1, 24, 64), (1, 1, 48, 96), (7, 4, 72, 96), (16, 5, 32, 128)])
-def test_mixture_of_experts_against_the_plain_one(dtype, tol, E, top, ff, width):
+@pytest.mark.parametrize("E,top,ff,width", [(4, 2, 40, 64), (6, 1, 24, 64), (1, 1, 48, 96), (7, 4, 72, 96), (16, 5, 32, 128),
+                                            (40, 7, 16, 64)])
+@pytest.mark.parametrize("T", [29, 300])
+def test_mixture_of_experts_against_the_plain_one(dtype, tol, E, top, ff, width, T):
+    """A few tokens (all experts on all tokens, the unchosen ones times zero) and a step of 300 tokens
+    (in bfloat16: rows sorted by expert, ragged groups, some experts with few rows or none)."""
     from tinyserve_b200.parts.moe import MixtureOfExperts
-    T = 29
     h = draws(T, width, seed=1)
     W = {"router": draws(E, width, seed=2, scale=0.5)}
     for e in range(E):
@@ -360,7 +363,18 @@ def test_mixture_of_experts_against_the_plain_one(dtype, tol, E, top, ff, width)
     from tinyserve_b200.kernels import ops
     got = ops.materialize(part.forward(on_device(h, dtype), None))
     want = plain.experts(h, W, "", {"router": {"experts": E, "top": top}})
-    assert (got.double().cpu() - want).abs().max() <= tol * want.abs().max()
+    # (in bfloat16 a token whose router scores are a rounding apart may take another expert: one row in fifty may differ)
+    err = (got.double().cpu() - want).abs().max(-1).values
+    allowed = T // 50 if dtype == torch.bfloat16 else 0
+    assert int((err > tol * want.abs().max()).sum()) <= allowed
+    if dtype == torch.bfloat16 and T >= ops.MOE_GROUPED_MIN_TOKENS and top < E:
+        # the other form on the same input: all experts on all tokens
+        keep, ops.MOE_GROUPED_MIN_TOKENS = ops.MOE_GROUPED_MIN_TOKENS, 10 ** 9
+        try:
+            dense = ops.materialize(part.forward(on_device(h, dtype), None))
+        finally:
+            ops.MOE_GROUPED_MIN_TOKENS = keep
+        assert (got.double() - dense.double()).abs().max() <= tol * want.abs().max(), "both forms route alike and agree to a rounding"
 
 
 # ----------------------------------------------------------------------------- whole models
