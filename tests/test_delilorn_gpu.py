@@ -342,6 +342,14 @@ def test_router_keeps_the_largest_probabilities_as_they_are(E, top):
     want[4, :top] = 1.0 / E
     assert (gates - want).abs().max() < 1e-6
     assert ((gates > 0).sum(-1) == top).all()
+    # the activation kernel routes by itself when it gets the logits: the same numbers in one launch
+    for dtype in (torch.float32, torch.bfloat16):
+        a = draws(33, E * 24, seed=3)
+        two = ops.moe_activate_(on_device(a, dtype), ops.moe_route(on_device(z, torch.float32), top), E)
+        one = ops.moe_activate_(on_device(a, dtype), None, E, logits=on_device(z, torch.float32), top=top)
+        assert torch.equal(one, two)
+        expect = torch.relu(a).pow(2).view(33, E, 24) * want[:, :, None]
+        assert (one.double().cpu().view(33, E, 24) - expect).abs().max() <= (1e-6 if dtype == torch.float32 else 8e-3) * expect.abs().max()
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])

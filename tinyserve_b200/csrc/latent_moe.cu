@@ -147,14 +147,8 @@ __global__ void gate_heads_kernel(const T* __restrict__ x, const T* __restrict__
 
 // ------------------------------------------------------------------ mixture of experts
 // a warp per token: probabilities of all experts, the `top` largest kept (ties: the lower number)
-__global__ void moe_route_kernel(const float* __restrict__ logits, float* __restrict__ gates, int num_tokens, int E, int top) {
-  pdl_trigger();
-  pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= num_tokens) return;
-  const float* z = logits + (size_t)t * E;
-  float* g = gates + (size_t)t * E;
+// one warp, one token: z [E] logits -> g [E] (global or shared memory)
+__device__ __forceinline__ void route_token(const float* __restrict__ z, float* g, int E, int top, int lane) {
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
   mx = warp_max(mx);
@@ -184,6 +178,15 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, float* __rest
     if (g[e] < 0.f) g[e] = 0.f;
 }
 
+__global__ void moe_route_kernel(const float* __restrict__ logits, float* __restrict__ gates, int num_tokens, int E, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= num_tokens) return;
+  route_token(logits + (size_t)t * E, gates + (size_t)t * E, E, top, lane);
+}
+
 // 16 bytes of a row as floats and back
 template <typename T> struct Chunk { static constexpr int N = 16 / sizeof(T); };
 template <typename T>
@@ -203,12 +206,21 @@ __device__ __forceinline__ void chunk_store(T* p, const float (&v)[Chunk<T>::N])
 }
 
 // a[t, e * ff + j] <- relu(a)^2 * gates[t, e]; VEC: 16 bytes a thread (ff a multiple of the chunk)
+// With `logits` (and top > 0) the block routes its token itself first (its first warp, into shared
+// memory): one launch for the router's softmax, its choice and the activation.
 template <typename T, bool VEC>
-__global__ void moe_activate_kernel(T* __restrict__ a, const float* __restrict__ gates, int E, int ff) {
+__global__ void moe_activate_kernel(T* __restrict__ a, const float* __restrict__ gates, int E, int ff,
+                                    const float* __restrict__ logits, int top) {
+  extern __shared__ float routed[];      // [E] when the kernel routes
   pdl_trigger();
   pdl_wait();
   const size_t t = blockIdx.x;
   T* row = a + t * (size_t)E * ff;
+  if (logits) {
+    if (threadIdx.x < 32) route_token(logits + t * E, routed, E, top, threadIdx.x);
+    __syncthreads();
+    gates = routed - t * E;              // the loops below index gates[t * E + e]
+  }
   if constexpr (VEC) {
     constexpr int N = Chunk<T>::N;
     const int per_expert = ff / N;
@@ -459,15 +471,19 @@ TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, in
   return 0;
 }
 
-TS_EXPORT int ts_moe_activate(int dtype, void* a, const float* gates, int num_tokens, int E, int ff, cudaStream_t stream) {
-  TS_REQUIRE(num_tokens > 0 && E > 0 && ff > 0 && a, "moe_activate: empty input");      // (gates null: the plain activation)
+// gates [tokens, E], or logits [tokens, E] with top > 0 (the kernel routes), or neither (the plain activation)
+TS_EXPORT int ts_moe_activate(int dtype, void* a, const float* gates, int num_tokens, int E, int ff, const float* logits,
+                              int top, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && E > 0 && ff > 0 && a, "moe_activate: empty input");
+  TS_REQUIRE(!(gates && logits) && (logits == nullptr || (top > 0 && top <= E && E <= 8192)), "moe_activate: gates or logits with top of %d experts", E);
+  const size_t smem = logits ? (size_t)E * sizeof(float) : 0;
   const bool vec = (uintptr_t)a % 16 == 0 && ff % (dtype == TS_F32 ? 4 : 8) == 0;
   if (dtype == TS_F32) {
-    if (vec) TS_LAUNCH("moe_activate", (moe_activate_kernel<float, true>), num_tokens, 256, 0, stream, (float*)a, gates, E, ff);
-    else TS_LAUNCH("moe_activate", (moe_activate_kernel<float, false>), num_tokens, 256, 0, stream, (float*)a, gates, E, ff);
+    if (vec) TS_LAUNCH("moe_activate", (moe_activate_kernel<float, true>), num_tokens, 256, smem, stream, (float*)a, gates, E, ff, logits, top);
+    else TS_LAUNCH("moe_activate", (moe_activate_kernel<float, false>), num_tokens, 256, smem, stream, (float*)a, gates, E, ff, logits, top);
   } else if (dtype == TS_BF16) {
-    if (vec) TS_LAUNCH("moe_activate", (moe_activate_kernel<__nv_bfloat16, true>), num_tokens, 256, 0, stream, (__nv_bfloat16*)a, gates, E, ff);
-    else TS_LAUNCH("moe_activate", (moe_activate_kernel<__nv_bfloat16, false>), num_tokens, 256, 0, stream, (__nv_bfloat16*)a, gates, E, ff);
+    if (vec) TS_LAUNCH("moe_activate", (moe_activate_kernel<__nv_bfloat16, true>), num_tokens, 256, smem, stream, (__nv_bfloat16*)a, gates, E, ff, logits, top);
+    else TS_LAUNCH("moe_activate", (moe_activate_kernel<__nv_bfloat16, false>), num_tokens, 256, smem, stream, (__nv_bfloat16*)a, gates, E, ff, logits, top);
   } else {
     return ts_fail("moe_activate: unknown dtype %d", dtype);
   }

@@ -1471,15 +1471,19 @@ def moe_route(logits, top):
     return gates
 
 
-def moe_activate_(a, gates, num_experts):
-    """a [T, E * ff] (in place) <- relu(a)^2 * gates[t, e] for the columns of expert e."""
-    _cuda(a, gates)
+def moe_activate_(a, gates, num_experts, logits=None, top=0):
+    """a [T, E * ff] (in place) <- relu(a)^2 * gates[t, e] for the columns of expert e.  With ``logits``
+    (float32 [T, E]) and ``top`` in place of ``gates`` the kernel routes every token itself first, as
+    ``moe_route`` does: one launch for softmax, choice and activation."""
+    _cuda(a, gates, logits)
     T = a.shape[0]
-    if not a.is_contiguous() or a.shape[1] % num_experts or gates.shape != (T, num_experts) or gates.dtype != torch.float32:
+    given = gates if gates is not None else logits
+    if (gates is None) == (logits is None) or not a.is_contiguous() or a.shape[1] % num_experts \
+            or given.shape != (T, num_experts) or given.dtype != torch.float32 or not given.is_contiguous():
         raise ValueError("moe_activate: operands do not fit")
     lib = _latent_moe()
     _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), _ptr(gates), c_int(T), c_int(num_experts),
-                                    c_int(a.shape[1] // num_experts), _stream()))
+                                    c_int(a.shape[1] // num_experts), _ptr(logits), c_int(top), _stream()))
     return a
 
 
@@ -1509,7 +1513,7 @@ def moe_grouped(h, gates, up, down_side_by_side, top):
     x = torch.empty(capacity, n, dtype=h.dtype, device=h.device)
     _check(lib, lib.ts_moe_gather(c_int(_dt(h)), _ptr(h), _ptr(row_token), _ptr(x), c_int(capacity), c_int(n), _stream()))
     a = torch.nn.functional.grouped_mm(x, up.view(E, ff, n).transpose(1, 2), offs=ends)
-    _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), None, c_int(capacity), c_int(1), c_int(ff), _stream()))
+    _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), None, c_int(capacity), c_int(1), c_int(ff), None, c_int(0), _stream()))
     y = torch.nn.functional.grouped_mm(a, down_side_by_side.view(n, E, ff).permute(1, 2, 0), offs=ends)
     out = torch.empty(T, n, dtype=h.dtype, device=h.device)
     _check(lib, lib.ts_moe_combine(c_int(_dt(y)), _ptr(y), _ptr(gates), _ptr(pair_row), _ptr(out), c_int(T), c_int(E), c_int(n),

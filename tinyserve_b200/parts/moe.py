@@ -55,12 +55,12 @@ class MixtureOfExperts(FeedForward):
 
     def forward(self, h, ctx):
         logits = ops.linear(h, self.w["router.weight"], out_float32=True)
-        gates = ops.moe_route(logits, self.top)
         if (h.dtype == ops.torch.bfloat16 and self.top < self.num_experts and h.shape[0] >= ops.MOE_GROUPED_MIN_TOKENS
                 and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0):
+            gates = ops.moe_route(logits, self.top)
             return ops.moe_grouped(h, gates, self.w["up.weight"], self.w["down.weight"], self.top)
         a = ops.materialize(ops.linear(h, self.w["up.weight"]))
-        ops.moe_activate_(a, gates, self.num_experts)
+        ops.moe_activate_(a, None, self.num_experts, logits=logits, top=self.top)      # (routes in the same kernel)
         return ops.linear(a, self.w["down.weight"], allow_pending=True)
 
 
