@@ -594,5 +594,46 @@ def test_greedy_generation_through_the_scheduler(tmp_path):
             ids.append(tok)
 
 
+def test_programs_replay_and_generate(tmp_path):
+    """bin/trace_run and ``python -m tinyserve_b200 generate`` as programs on a Delilorn folder: the
+    architecture is chosen by config.json; stdin to files, 'done' lines, exit code 0; greedy tokens."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = make_delilorn_dir(tmp_path / "m", "Q", seed=2)
+    cfg, weights = plain.load_folder(folder)
+    reqs = {"p": random_ids(cfg["vocab"], 45, seed=1), "q": random_ids(cfg["vocab"], 30, seed=2)}
+    steps = schedule_mixed(reqs, max_live=2, seed=0)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+         "--out", str(out), "--max-tokens", str(max_live_tokens(steps))],
+        input="\n".join(lines_of(steps)) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    outputs = {}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        outputs[s["step"]] = torch.from_numpy(np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(wanted, cfg["vocab"]))
+    got = collect_logits(steps, outputs, cfg["vocab"])
+    for rid, ids in reqs.items():
+        ref = plain.logits(cfg, weights, ids)
+        assert (got[rid].double() - ref).abs().max().item() < TOLERANCE["float32"] * ref.abs().max().item()
+    prompt = reqs["q"][:9]
+    proc = subprocess.run(
+        [sys.executable, "-m", "tinyserve_b200", "generate", "--model", folder, "--dtype", "float32", "--prompt-ids",
+         ",".join(map(str, prompt)), "--max-tokens", "5", "--repetition-penalty", "1.0", "--ignore-eos", "--max-model-len", "64",
+         "--max-num-seqs", "2", "--max-num-batched-tokens", "32", "--num-blocks", "16", "--block-size", "16"],
+        capture_output=True, text=True, timeout=600, cwd=root)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    tokens = [int(t) for t in proc.stdout.strip().split("\n")[-1].split()]
+    want, gaps = plain.greedy(cfg, weights, prompt, 5)
+    for a, b, gap in zip(tokens, want, gaps):
+        if gap < 1e-3:
+            break
+        assert a == b, (tokens, want)
+    assert len(tokens) == 5
+
+
 def test_measured_differences_are_reported():
     print({k: (f"{v[0]:.2e}", f"{v[1]:.2e}") for k, v in sorted(MEASURED.items())})
