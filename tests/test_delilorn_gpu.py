@@ -565,6 +565,33 @@ def test_far_keys_window_edges_sinks_and_long_memories(dtype, name, tmp_path):
           slack=slack, max_live=3)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_head_sizes_of_real_models(dtype, tmp_path):
+    """Cache rows of 256 and of 128, attention heads of 128 behind a window beside kept tokens, state heads
+    of 128 x 256, pages of 64: the kernels that real layer sizes reach (tcgen05 prefill, mma.sync with wide
+    heads, decode by whole pages), prompts longer than two key tiles of any kernel."""
+    from delilorn_configs import _latent, _moe
+    from tinyserve_b200.config import config_from_dict
+    from tinyserve_b200.weights import write_random_model
+    raw = {"architecture": "Delilorn", "vocab": 1000, "width": 512, "norm": {"eps": 1e-6}, "layers": [
+        {"type": "latent_attention", "mlp": _moe(256, 8, 2), "mixer": _latent(4, 128, 64, 128, 256, 192, 0.08, 1e4)},
+        {"type": "lightning", "mlp": _moe(256, 8, 2), "mixer": {"heads": 2, "dim": 128, "vdim": 256, "decay": [0.97, 0.999]}},
+        {"type": "latent_attention", "mlp": _moe(256, 8, 2), "mixer": _latent(4, 128, 32, 128, 256, 96, 0.08, 1e4)},
+        {"type": "attention", "mlp": _moe(256, 8, 2), "mixer": {
+            "heads": 4, "kv_heads": 1, "dim": 128, "vdim": 128, "scale": 0.09,
+            "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 256}},
+            "mask": {"size": 150, "keep_first": 4}}},
+        {"type": "latent_attention", "mlp": None, "mixer": _latent(8, 64, 64, 64, 128, 192, 0.1, 1e4, kv_from=0)},
+    ]}
+    folder = decisive_routers(write_random_model(config_from_dict(raw), str(tmp_path / "model"), seed=5))
+    cfg, weights = plain.load_folder(folder)
+    reqs = {"a": random_ids(1000, 420, seed=1), "b": random_ids(1000, 130, seed=2)}
+    ref = {rid: plain.logits(cfg, weights, ids) for rid, ids in reqs.items()}
+    model = {"name": "real", "folder": folder, "cfg": cfg, "requests": reqs, "ref": ref}
+    check(model, dtype, schedule_tail_decode(reqs, 40), tmp_path / "tail", page=64)
+    check(model, dtype, schedule_mixed(reqs, max_live=2, seed=1, chunk_sizes=(200, 2, 129, 64, 1)), tmp_path / "mixed", max_live=2)
+
+
 # ----------------------------------------------------------------------------- the entry point
 def test_greedy_generation_through_the_scheduler(tmp_path):
     """Five prompts of unequal length through LLM.generate with three state slots and a budget of
