@@ -594,7 +594,7 @@ def test_head_sizes_of_real_models(dtype, tmp_path):
 
 # ----------------------------------------------------------------------------- the entry point
 def test_greedy_generation_through_the_scheduler(tmp_path):
-    """Five prompts of unequal length through LLM.generate with three state slots and a budget of
+    """Five prompts of unequal length through LLM.generate with three state slots and at most
     48 tokens a step (prompts in portions beside decoding requests, slots and pages used again)."""
     from tinyserve_b200 import LLM, SamplingParams
     folder = make_delilorn_dir(tmp_path, "P", seed=44)

@@ -12,6 +12,8 @@ experts' weights anyway) and how the 32-bit engine runs; a bfloat16 step of many
 rows by expert instead, so that an expert multiplies its own rows only (``ops.moe_grouped``)."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from .base import FeedForward, ParamSpec, Source, register_feed_forward
 
@@ -55,7 +57,7 @@ class MixtureOfExperts(FeedForward):
 
     def forward(self, h, ctx):
         logits = ops.linear(h, self.w["router.weight"], out_float32=True)
-        if (h.dtype == ops.torch.bfloat16 and self.top < self.num_experts and h.shape[0] >= ops.MOE_GROUPED_MIN_TOKENS
+        if (h.dtype == torch.bfloat16 and self.top < self.num_experts and h.shape[0] >= ops.MOE_GROUPED_MIN_TOKENS
                 and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0):
             gates = ops.moe_route(logits, self.top)
             return ops.moe_grouped(h, gates, self.w["up.weight"], self.w["down.weight"], self.top)
