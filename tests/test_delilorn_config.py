@@ -48,6 +48,14 @@ def test_a_damaged_configuration_is_refused(damage, text):
         config_from_dict(raw)
 
 
+def test_a_reader_of_another_cache_may_leave_the_row_sizes_out():
+    from tinyserve_b200.config import config_from_dict
+    raw = delilorn_config_dict("P")
+    for key in ("kv_rank", "rot_dim", "rot"):
+        del raw["layers"][3]["mixer"][key]
+    assert config_from_dict(raw) == delilorn_config("P")
+
+
 def test_run_order_caches_and_states():
     from tinyserve_b200.parts import build_model
     p = build_model(delilorn_config("P"))

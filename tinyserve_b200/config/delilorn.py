@@ -78,6 +78,13 @@ class DelilornConfig(ModelConfig):
                         any(isinstance(d, bool) or not isinstance(d, (int, float)) for d in decay):
                     raise ConfigError(f"config.json: {at}.decay must list one decay per head")
             elif kind == "latent_attention":
+                source = mixer.get("kv_from")
+                if isinstance(source, int) and not isinstance(source, bool) and 0 <= source < i \
+                        and layers[source]["type"] == "latent_attention":
+                    # what the cache row is made of is the writer's to say; a reader may leave it out
+                    for key in ("kv_rank", "rot_dim", "rot"):
+                        if key not in mixer and key in layers[source]["mixer"]:
+                            mixer[key] = copy.deepcopy(layers[source]["mixer"][key])
                 for key in ("q_rank", "kv_rank"):
                     _positive_int(mixer, key, at)
                 rot_dim = mixer.get("rot_dim", 0)
