@@ -105,6 +105,7 @@ class DelilornConfig(ModelConfig):
                     if any(other["mixer"].get(k) != mixer.get(k) for k in ("kv_rank", "rot_dim", "rot")):
                         raise ConfigError(f"config.json: {at}.kv_from: layer {source} differs in kv_rank, rot_dim or rot")
             else:
+                mixer.setdefault("kv_heads", mixer["heads"])        # (left out: every query head has its own)
                 kv_heads = _positive_int(mixer, "kv_heads", at)
                 if mixer["heads"] % kv_heads:
                     raise ConfigError(f"config.json: {at}: heads is no multiple of kv_heads")
